@@ -1,0 +1,48 @@
+// Host-side helpers shared by the C-ABI translation units: thread-local error text, CUDA error checks and the
+// TMA tensor-map encoder (driver entry point fetched at run time, so the library has no link dependency on libcuda
+// and loads on machines without a GPU).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/b200fa.h"
+#include "attn_index.h"
+
+namespace b200fa {
+
+void set_error(const char* format, ...);
+
+#define B200FA_CUDA_CHECK(call)                                                             \
+  do {                                                                                      \
+    cudaError_t status_ = (call);                                                           \
+    if (status_ != cudaSuccess) {                                                           \
+      ::b200fa::set_error("%s failed: %s (%s:%d)", #call, cudaGetErrorString(status_), __FILE__, __LINE__); \
+      return B200FA_ERR_CUDA;                                                               \
+    }                                                                                       \
+  } while (0)
+
+#define B200FA_REQUIRE(condition, ...)      \
+  do {                                      \
+    if (!(condition)) {                     \
+      ::b200fa::set_error(__VA_ARGS__);     \
+      return B200FA_ERR_INVALID;            \
+    }                                       \
+  } while (0)
+
+// 4-D tensor map over a (batch, row, head, column) tensor of `element_bytes`-wide elements with strides in elements.
+// Box = (box_cols, 1 head, box_rows, 1 batch); swizzle 128 B when box_cols * element_bytes == 128.
+int encode_tensor_map(CUtensorMap* map, const void* base, CUtensorMapDataType type, int element_bytes, int64_t cols,
+                      int64_t heads, int64_t rows, int64_t batch, int64_t head_stride, int64_t row_stride,
+                      int64_t batch_stride, int box_cols, int box_rows);
+
+Problem to_problem(const b200fa_problem& in);
+
+int device_sm_count(int* count);
+
+// Device address of the library's status word on the current device (null + error text on failure).
+int* device_status_word();
+
+}  // namespace b200fa

@@ -1,0 +1,502 @@
+// Forward attention kernel for sm_100a: O = softmax(scale Q K^T + mask) V and the row log-sum-exp.
+//
+// Takes the place of the reference's flash_attn_fwd for sm_100 (zig/flash_fwd_sm100.zig:41-1380) and of its
+// persistent inter-sequence forward (zig/inter_sequence_forward_sm100.zig:40-1274); one kernel serves fixed-length,
+// packed (varlen) and inter-sequence problems because key blocks come from the KeyCursor of attn_index.h.
+//
+// One persistent CTA per SM. A work item is 256 query rows of one head (two 128-row MMA tiles, "stages").
+// Warp roles: warps 0-3 softmax of stage 0, warps 4-7 softmax of stage 1 (one thread per query row, TMEM lane =
+// row), warp 8 issues tcgen05 MMAs, warp 9 issues TMA loads.
+//   S_i = Q_i K_j^T   SS-MMA 128x128xD  into TMEM columns [128 i, 128 i + 128)
+//   P_i               BF16, written by the softmax warps over the first 64 columns of S_i
+//   O_i += P_i V_j    TS-MMA 128xDx128 (A from TMEM) into TMEM columns [256 + D i, 256 + D i + D)
+// Q tiles, and a ring of K/V tiles, are TMA-loaded into 128-byte swizzled shared memory and tracked by mbarriers.
+// Softmax runs in the log2 domain with a lazy rescale: the running reference maximum only moves when the block
+// maximum exceeds it by more than 8 (in log2 units), so O is almost never rescaled (reference
+// zig/flash_fwd_sm100.zig:963-976).
+#include "common.h"
+#include "ptx.cuh"
+
+namespace b200fa {
+
+struct FwdParams {
+  Problem prob;
+  float scale_log2;
+  __nv_bfloat16* o;
+  int64_t o_batch_stride, o_row_stride, o_head_stride;
+  float* lse;
+  int64_t lse_batch_stride, lse_head_stride;
+  const int2* work_list;  // packed problems: (sequence, block) per entry; null for fixed length
+  int m_blocks;           // fixed length: work items per (batch, head)
+  int num_tiles;
+  int* status;            // device status word of the library
+};
+
+template <int D>
+struct FwdConfig {
+  static constexpr int kStages = D <= 64 ? 6 : 4;             // K/V ring slots
+  static constexpr int kTileBytes = kBlockM * D * 2;           // one 128 x D BF16 tile
+  static constexpr int kHalves = D / 64;                       // 64-column (128-byte) swizzle panels per tile
+  static constexpr int kPanelBytes = kBlockM * 128;
+  static constexpr int kSmemQ = 2 * kTileBytes;
+  static constexpr int kSmemKv = kStages * kTileBytes;
+  static constexpr int kSmemBytes = kSmemQ + kSmemKv + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kThreads = 320;
+  static constexpr int kTmemS = 0;
+  static constexpr int kTmemO = 256;
+};
+
+struct FwdTile {
+  int seq, head, kv_head, m0;
+  SeqInfo s;
+  bool valid;
+};
+
+__device__ __forceinline__ FwdTile decode_tile(const FwdParams& p, int tile) {
+  FwdTile t;
+  const Problem& pr = p.prob;
+  if (p.work_list) {
+    int entry = tile / pr.heads_q;
+    t.head = tile - entry * pr.heads_q;
+    int2 e = p.work_list[entry];
+    t.seq = e.x;
+    t.m0 = e.y * kFwdTileM;
+    t.valid = e.x < pr.batch;
+  } else {
+    int per_block = pr.batch * pr.heads_q;
+    int mb = tile / per_block;
+    int rem = tile - mb * per_block;
+    t.seq = rem / pr.heads_q;
+    t.head = rem - t.seq * pr.heads_q;
+    t.m0 = (p.m_blocks - 1 - mb) * kFwdTileM;
+    t.valid = true;
+  }
+  t.kv_head = t.head / (pr.heads_q / pr.heads_kv);
+  if (t.valid) t.s = seq_info(pr, t.seq);
+  return t;
+}
+
+template <int D>
+__global__ void __launch_bounds__(FwdConfig<D>::kThreads, 1)
+fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+           const __grid_constant__ CUtensorMap map_v, const __grid_constant__ FwdParams p) {
+  using Cfg = FwdConfig<D>;
+  constexpr int NS = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t smem_q = smem_base;
+  const uint32_t smem_kv = smem_base + Cfg::kSmemQ;
+  const uint32_t bar_base = smem_kv + Cfg::kSmemKv;
+  // barrier layout (8 bytes each)
+  const uint32_t bar_q_full = bar_base;            // [2]
+  const uint32_t bar_q_empty = bar_base + 16;      // [1]
+  const uint32_t bar_kv_full = bar_base + 24;      // [NS]
+  const uint32_t bar_kv_empty = bar_kv_full + 8 * NS;
+  const uint32_t bar_s_full = bar_kv_empty + 8 * NS;   // [2]
+  const uint32_t bar_p_full = bar_s_full + 16;         // [2]
+  const uint32_t bar_pv_done = bar_p_full + 16;        // [2]
+  const uint32_t tmem_slot = bar_pv_done + 16;         // 4 bytes
+  const uint32_t abort_slot = tmem_slot + 4;           // 4 bytes
+  volatile int* abort_flag =
+      reinterpret_cast<volatile int*>(smem_raw + (abort_slot - smem_u32(smem_raw)));
+  volatile uint32_t* tmem_ptr_smem =
+      reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+  const WaitCtx wctx{abort_flag, p.status};
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(bar_q_full, 1);
+    mbar_init(bar_q_full + 8, 1);
+    mbar_init(bar_q_empty, 1);
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(bar_kv_full + 8 * i, 1);
+      mbar_init(bar_kv_empty + 8 * i, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_s_full + 8 * i, 1);
+      mbar_init(bar_p_full + 8 * i, 128);
+      mbar_init(bar_pv_done + 8 * i, 1);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  if (warp == 9 && lane == 0) {
+    tma_prefetch_descriptor(&map_q);
+    tma_prefetch_descriptor(&map_k);
+    tma_prefetch_descriptor(&map_v);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+  const Problem& pr = p.prob;
+
+  if (warp == 9) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t ring = 0;      // K/V slots issued so far
+      uint32_t q_count = 0;   // tiles with at least one key block
+      bool ok = true;
+      auto load_tile = [&](const CUtensorMap* map, uint32_t dst, uint32_t bar, int head, int row, int batch_coord) {
+        mbar_expect_tx(bar, Cfg::kTileBytes);
+#pragma unroll
+        for (int h = 0; h < Cfg::kHalves; ++h) tma_load_4d(dst + h * Cfg::kPanelBytes, map, bar, h * 64, head, row, batch_coord);
+      };
+      auto load_kv = [&](const CUtensorMap* map, int head, int row, int batch_coord) -> bool {
+        uint32_t slot = ring % NS, phase = (ring / NS) & 1;
+        if (!mbar_wait(bar_kv_empty + 8 * slot, phase ^ 1, wctx, kWaitKvEmpty)) return false;
+        load_tile(map, smem_kv + slot * Cfg::kTileBytes, bar_kv_full + 8 * slot, head, row, batch_coord);
+        ++ring;
+        return true;
+      };
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        FwdTile t = decode_tile(p, tile);
+        if (!t.valid) continue;
+        KeyCursor cur;
+        cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kFwdTileM, t.s.lq));
+        OtherBlock kb;
+        if (!cur.next(&kb)) continue;
+        if (!mbar_wait(bar_q_empty, (q_count & 1) ^ 1, wctx, kWaitQEmpty)) { ok = false; break; }
+        ++q_count;
+        load_tile(&map_q, smem_q, bar_q_full, t.head, t.s.q0 + t.m0, t.s.batch_coord);
+        if (!load_kv(&map_k, t.kv_head, kb.row, t.s.batch_coord)) { ok = false; break; }
+        load_tile(&map_q, smem_q + Cfg::kTileBytes, bar_q_full + 8, t.head, t.s.q0 + t.m0 + kBlockM, t.s.batch_coord);
+        for (;;) {
+          if (!load_kv(&map_v, t.kv_head, kb.row, t.s.batch_coord)) { ok = false; break; }
+          if (!cur.next(&kb)) break;
+          if (!load_kv(&map_k, t.kv_head, kb.row, t.s.batch_coord)) { ok = false; break; }
+        }
+      }
+    }
+  } else if (warp == 8) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(kBlockM, kBlockN, 0, 0);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(kBlockM, D, 0, 1);
+      uint32_t ring = 0, q_count = 0, blocks = 0;
+      bool ok = true;
+      auto issue_s = [&](int stage, uint32_t k_smem) {
+        const uint32_t q_addr = smem_q + stage * Cfg::kTileBytes;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * Cfg::kPanelBytes + (kk & 3) * 32;
+          umma_ss(tmem_base + Cfg::kTmemS + stage * 128, umma_smem_desc(q_addr + off, 16, 1024),
+                  umma_smem_desc(k_smem + off, 16, 1024), idesc_s, kk > 0);
+        }
+      };
+      auto issue_pv = [&](int stage, uint32_t v_smem, bool accumulate) {
+#pragma unroll
+        for (int kk = 0; kk < kBlockN / 16; ++kk) {
+          umma_ts(tmem_base + Cfg::kTmemO + stage * D, tmem_base + Cfg::kTmemS + stage * 128 + kk * 8,
+                  umma_smem_desc(v_smem + kk * 2048, Cfg::kPanelBytes, 1024), idesc_pv, accumulate || kk > 0);
+        }
+      };
+      auto wait_kv = [&](uint32_t index) -> bool {
+        return mbar_wait(bar_kv_full + 8 * (index % NS), (index / NS) & 1, wctx, kWaitKvFull);
+      };
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        FwdTile t = decode_tile(p, tile);
+        if (!t.valid) continue;
+        KeyCursor cur;
+        cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kFwdTileM, t.s.lq));
+        OtherBlock kb;
+        if (!cur.next(&kb)) continue;
+        const uint32_t q_phase = q_count & 1;
+        ++q_count;
+        uint32_t k_index = ring++;
+        if (!mbar_wait(bar_q_full, q_phase, wctx, kWaitQFull) || !wait_kv(k_index)) { ok = false; break; }
+        tc_fence_after();
+        issue_s(0, smem_kv + (k_index % NS) * Cfg::kTileBytes);
+        tc_commit(bar_s_full);
+        if (!mbar_wait(bar_q_full + 8, q_phase, wctx, kWaitQFull)) { ok = false; break; }
+        tc_fence_after();
+        issue_s(1, smem_kv + (k_index % NS) * Cfg::kTileBytes);
+        tc_commit(bar_s_full + 8);
+        tc_commit(bar_kv_empty + 8 * (k_index % NS));
+        bool first = true;
+        for (;;) {
+          const bool more = cur.next(&kb);
+          const uint32_t v_index = ring++;
+          if (!wait_kv(v_index)) { ok = false; break; }
+          if (more) {
+            k_index = ring++;
+            if (!wait_kv(k_index)) { ok = false; break; }
+          }
+          const uint32_t v_smem = smem_kv + (v_index % NS) * Cfg::kTileBytes;
+          const uint32_t k_smem = smem_kv + (k_index % NS) * Cfg::kTileBytes;
+          const uint32_t phase = blocks & 1;
+          if (!mbar_wait(bar_p_full, phase, wctx, kWaitPFull)) { ok = false; break; }
+          tc_fence_after();
+          issue_pv(0, v_smem, !first);
+          tc_commit(bar_pv_done);
+          if (more) {
+            issue_s(0, k_smem);
+            tc_commit(bar_s_full);
+          }
+          if (!mbar_wait(bar_p_full + 8, phase, wctx, kWaitPFull)) { ok = false; break; }
+          tc_fence_after();
+          issue_pv(1, v_smem, !first);
+          tc_commit(bar_pv_done + 8);
+          tc_commit(bar_kv_empty + 8 * (v_index % NS));
+          if (more) {
+            issue_s(1, k_smem);
+            tc_commit(bar_s_full + 8);
+            tc_commit(bar_kv_empty + 8 * (k_index % NS));
+          } else {
+            tc_commit(bar_q_empty);
+          }
+          ++blocks;
+          first = false;
+          if (!more) break;
+        }
+      }
+      // The last commit of this thread must land before the CTA may exit.
+      if (ok && q_count > 0) mbar_wait(bar_q_empty, (q_count - 1) & 1, wctx, kWaitQEmpty);
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue (one thread per row)
+    const int stage = warp >> 2;
+    const int row_in_stage = (warp & 3) * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t t_s = tmem_base + lane_addr + Cfg::kTmemS + stage * 128;
+    const uint32_t t_o = tmem_base + lane_addr + Cfg::kTmemO + stage * D;
+    const uint32_t my_s_full = bar_s_full + 8 * stage;
+    const uint32_t my_p_full = bar_p_full + 8 * stage;
+    const uint32_t my_pv_done = bar_pv_done + 8 * stage;
+    const float scale_log2 = p.scale_log2;
+    uint32_t blocks = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      FwdTile t = decode_tile(p, tile);
+      if (!t.valid) continue;
+      const int row = t.m0 + stage * kBlockM + row_in_stage;  // row within the sequence
+      KeyCursor cur;
+      cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kFwdTileM, t.s.lq));
+      const int band_lo = cur.band.lo(row), band_hi = cur.band.hi(row);
+      float m = -INFINITY, l = 0.f;
+      int tile_blocks = 0;
+      OtherBlock kb;
+      while (cur.next(&kb)) {
+        if (!mbar_wait_warp(my_s_full, blocks & 1, wctx, kWaitSFull)) { ok = false; break; }
+        tc_fence_after();
+        float s[128];
+        {
+          uint32_t* r = reinterpret_cast<uint32_t*>(s);
+          tmem_ld32(t_s, r);
+          tmem_ld32(t_s + 32, r + 32);
+          tmem_ld32(t_s + 64, r + 64);
+          tmem_ld32(t_s + 96, r + 96);
+          tc_wait_ld();
+        }
+        int lo, hi;
+        if (kb.banded) {
+          lo = band_lo - kb.col0;
+          hi = band_hi - kb.col0;
+        } else {
+          lo = 0;
+          hi = kb.limit - kb.col0;
+        }
+        if (__any_sync(0xffffffffu, lo > 0 || hi < kBlockN)) {
+#pragma unroll
+          for (int c = 0; c < 128; ++c) s[c] = (c >= lo && c < hi) ? s[c] : -INFINITY;
+        }
+        float bm0 = s[0], bm1 = s[1], bm2 = s[2], bm3 = s[3];
+#pragma unroll
+        for (int c = 4; c < 128; c += 4) {
+          bm0 = fmaxf(bm0, s[c]);
+          bm1 = fmaxf(bm1, s[c + 1]);
+          bm2 = fmaxf(bm2, s[c + 2]);
+          bm3 = fmaxf(bm3, s[c + 3]);
+        }
+        const float m_new = fmaxf(m, fmaxf(fmaxf(bm0, bm1), fmaxf(bm2, bm3)));
+        const bool grow = (m_new - m) * scale_log2 > 8.f;  // also true when m is -inf and m_new is finite
+        if (__any_sync(0xffffffffu, grow)) {
+          float alpha = 1.f;
+          if (grow) {
+            alpha = (m == -INFINITY) ? 0.f : ex2_approx((m - m_new) * scale_log2);
+            l *= alpha;
+            m = m_new;
+          }
+          if (tile_blocks > 0) {
+            if (!mbar_wait_warp(my_pv_done, (blocks - 1) & 1, wctx, kWaitPvDone)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t o[32];
+              tmem_ld32(t_o + 32 * c, o);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st32(t_o + 32 * c, o);
+            }
+          }
+        }
+        const float mc = (m == -INFINITY) ? 0.f : m * scale_log2;
+        float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t packed[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = ex2_approx(fmaf(s[32 * c + 2 * i], scale_log2, -mc));
+            const float p1 = ex2_approx(fmaf(s[32 * c + 2 * i + 1], scale_log2, -mc));
+            l0 += p0;
+            l1 += p1;
+            packed[i] = pack_bf16x2(p0, p1);
+          }
+          tmem_st16(t_s + 16 * c, packed);
+        }
+        l += l0 + l1;
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(my_p_full);
+        ++blocks;
+        ++tile_blocks;
+      }
+      if (!ok) break;
+      // ---- epilogue: O / l -> BF16 -> global, lse
+      const bool row_valid = row < t.s.lq;
+      __nv_bfloat16* o_row = p.o + t.s.batch_coord * p.o_batch_stride + (int64_t)(t.s.q0 + row) * p.o_row_stride +
+                             (int64_t)t.head * p.o_head_stride;
+      float* lse_ptr = p.lse + t.s.batch_coord * p.lse_batch_stride + (int64_t)t.head * p.lse_head_stride + t.s.q0 + row;
+      if (tile_blocks == 0) {
+        if (row_valid) {
+          const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll
+          for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(o_row)[c] = zero;
+          *lse_ptr = -INFINITY;
+        }
+        continue;
+      }
+      if (!mbar_wait_warp(my_pv_done, (blocks - 1) & 1, wctx, kWaitEpilogue)) { ok = false; break; }
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(t_o + 32 * c, o);
+        tc_wait_ld();
+        if (row_valid) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(o[8 * i + 0]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
+            v.y = pack_bf16x2(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
+            v.z = pack_bf16x2(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
+            v.w = pack_bf16x2(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
+            reinterpret_cast<uint4*>(o_row)[4 * c + i] = v;
+          }
+        }
+      }
+      if (row_valid) {
+        const float mc = (m == -INFINITY) ? 0.f : m * scale_log2;
+        *lse_ptr = l > 0.f ? (mc + log2f(l)) * 0.69314718055994531f : -INFINITY;
+      }
+      tc_fence_before();
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (*abort_flag) {
+    // A wait ran out: give copies in flight time to land before the shared memory is released.
+    for (int i = 0; i < 50; ++i) __nanosleep(20000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 8) tmem_dealloc(tmem_base, 512);
+}
+
+// -------------------------------------------------------------------------------------------------- host side
+
+template <int D>
+static int launch_fwd_d(const b200fa_fwd_args& a, cudaStream_t stream) {
+  using Cfg = FwdConfig<D>;
+  const b200fa_problem& bp = a.problem;
+  const bool packed = bp.cu_seqlens_q != nullptr;
+  FwdParams p;
+  p.prob = to_problem(bp);
+  p.scale_log2 = bp.softmax_scale * 1.4426950408889634f;
+  p.o = static_cast<__nv_bfloat16*>(a.out);
+  p.o_batch_stride = packed ? 0 : a.out_stride[0];
+  p.o_row_stride = a.out_stride[1];
+  p.o_head_stride = a.out_stride[2];
+  p.lse = a.softmax_lse;
+  p.lse_batch_stride = packed ? 0 : a.lse_stride[0];
+  p.lse_head_stride = a.lse_stride[1];
+  p.work_list = nullptr;
+  p.m_blocks = 0;
+  p.status = device_status_word();
+  if (!p.status) return B200FA_ERR_CUDA;
+
+  const int64_t rows_q = bp.seqlen_q, rows_k = bp.seqlen_k;
+  const int64_t tensor_batch = packed ? 1 : bp.batch;
+  if (packed) {
+    const int64_t entries = work_list_entries(rows_q, bp.batch, kFwdTileM);
+    B200FA_REQUIRE(a.workspace_bytes >= b200fa_fwd_workspace_bytes(&bp) && (entries == 0 || a.workspace),
+                   "forward workspace is too small: need %zu bytes", b200fa_fwd_workspace_bytes(&bp));
+    if (entries == 0) return B200FA_OK;
+    const int32_t* other = bp.cu_visible_k ? bp.cu_visible_k : bp.cu_seqlens_k;
+    int status = b200fa_work_list(bp.cu_seqlens_q, other, bp.batch, kFwdTileM, 1, (int32_t)entries,
+                                  static_cast<int32_t*>(a.workspace), stream);
+    if (status != B200FA_OK) return status;
+    p.work_list = static_cast<const int2*>(a.workspace);
+    p.num_tiles = (int)(entries * bp.heads_q);
+  } else {
+    p.m_blocks = ceil_div(bp.seqlen_q, kFwdTileM);
+    p.num_tiles = p.m_blocks * bp.batch * bp.heads_q;
+  }
+  if (p.num_tiles <= 0 || rows_q == 0) return B200FA_OK;
+
+  CUtensorMap map_q, map_k, map_v;
+  int status = encode_tensor_map(&map_q, a.q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, bp.heads_q, rows_q, tensor_batch,
+                                 a.q_stride[2], a.q_stride[1], packed ? rows_q * a.q_stride[1] : a.q_stride[0], 64,
+                                 kBlockM);
+  if (status != B200FA_OK) return status;
+  // An empty key tensor still needs valid maps: give them one row of the query tensor (never read, no key blocks).
+  const bool no_keys = rows_k == 0;
+  const void* k_base = no_keys ? a.q : a.k;
+  const void* v_base = no_keys ? a.q : a.v;
+  const int64_t k_rows = no_keys ? 1 : rows_k;
+  status = encode_tensor_map(&map_k, k_base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, no_keys ? 1 : bp.heads_kv, k_rows,
+                             tensor_batch, no_keys ? D : a.k_stride[2], no_keys ? D : a.k_stride[1],
+                             no_keys ? D : (packed ? k_rows * a.k_stride[1] : a.k_stride[0]), 64, kBlockN);
+  if (status != B200FA_OK) return status;
+  status = encode_tensor_map(&map_v, v_base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, no_keys ? 1 : bp.heads_kv, k_rows,
+                             tensor_batch, no_keys ? D : a.v_stride[2], no_keys ? D : a.v_stride[1],
+                             no_keys ? D : (packed ? k_rows * a.v_stride[1] : a.v_stride[0]), 64, kBlockN);
+  if (status != B200FA_OK) return status;
+
+  static bool attribute_set = false;
+  if (!attribute_set) {
+    B200FA_CUDA_CHECK(cudaFuncSetAttribute(fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    attribute_set = true;
+  }
+  int sms = 0;
+  status = device_sm_count(&sms);
+  if (status != B200FA_OK) return status;
+  const int grid = p.num_tiles < sms ? p.num_tiles : sms;
+  fwd_kernel<D><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+  B200FA_CUDA_CHECK(cudaGetLastError());
+  return B200FA_OK;
+}
+
+int launch_fwd(const b200fa_fwd_args& a, cudaStream_t stream) {
+  switch (a.problem.head_dim) {
+    case 64:
+      return launch_fwd_d<64>(a, stream);
+    case 128:
+      return launch_fwd_d<128>(a, stream);
+    default:
+      set_error("head_dim %d is not supported by the forward kernel (supported: 64, 128)", a.problem.head_dim);
+      return B200FA_ERR_UNSUPPORTED;
+  }
+}
+
+}  // namespace b200fa
