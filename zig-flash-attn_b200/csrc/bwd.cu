@@ -1,8 +1,733 @@
+// Backward attention for sm_100a: preprocess, main dK/dV/dQ kernel, postprocess.
+//
+// Takes the place of the reference's flash_attn_bwd_preprocess (zig/flash_bwd_preprocess.zig:118-237), its sm_100
+// main kernels (zig/flash_bwd_sm100.zig:31-1097) and flash_attn_bwd_postprocess (zig/flash_bwd_postprocess.zig:139-347).
+//
+// Main kernel: one CTA per (128-key block, kv head, sequence). It keeps the K and V tiles of its block in shared
+// memory and walks every (query head of the group, 128-row query block) that can see the block (QueryCursor).
+// Scores are computed transposed, keys on the 128 TMEM lanes and queries on the columns:
+//   S^T  = K Q^T          SS-MMA  -> TMEM [0,128)            P^T  = exp2(S^T c - lse) (BF16, over S^T)
+//   dP^T = V dO^T         SS-MMA  -> TMEM [128,256)          dS^T = P^T o (dP^T - D)  (BF16, to shared memory)
+//   dV  += P^T dO         TS-MMA  -> TMEM [256,256+D)
+//   dK  += dS^T Q         SS-MMA  -> TMEM [256+D,256+2D)
+//   dQ   = dS K           SS-MMA  -> TMEM [128,128+D) (over dP^T), drained by the reduce warps into shared memory
+//                                    and added into the FP32 dQ accumulator with TMA reduce-add.
+// Warps 0-7 compute P and dS (two groups of four warps, 64 query columns each), warps 8-11 drain dQ, warp 12 issues
+// MMAs, warp 13 issues TMA loads and the asynchronous copies of the per-row statistics.
+#include <limits.h>
+
 #include "common.h"
+#include "ptx.cuh"
+
 namespace b200fa {
-size_t bwd_workspace_bytes(const b200fa_problem&) { return 0; }
-int launch_bwd(const b200fa_bwd_args&, cudaStream_t) {
-  set_error("backward not built yet");
-  return B200FA_ERR_UNSUPPORTED;
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct BwdParams {
+  Problem prob;
+  float scale, scale_log2;
+  const float* lse_log2;  // (heads_q, rows) : lse * log2(e), +inf for rows without keys
+  const float* dpsum;     // (heads_q, rows) : sum_d O * dO
+  int64_t rows;           // rows of the statistics / dQ accumulator per head (batch * seqlen_q or total_q)
+  __nv_bfloat16* dk;
+  __nv_bfloat16* dv;
+  int64_t dk_batch_stride, dk_row_stride, dk_head_stride;
+  int64_t dv_batch_stride, dv_row_stride, dv_head_stride;
+  const int2* work_list;  // packed problems: (key sequence, key block) per blockIdx.x
+  int* status;
+};
+
+template <int D>
+struct BwdConfig {
+  static constexpr int kTileBytes = 128 * D * 2;
+  static constexpr int kPanelBytes = 128 * 128;
+  static constexpr int kHalves = D / 64;
+  static constexpr int kDsBytes = 128 * 128 * 2;
+  static constexpr int kStageBytes = 128 * 32 * 4;
+  static constexpr int kOffK = 0;
+  static constexpr int kOffV = kOffK + kTileBytes;
+  static constexpr int kOffQ = kOffV + kTileBytes;       // two stages
+  static constexpr int kOffDo = kOffQ + 2 * kTileBytes;
+  static constexpr int kOffDs = kOffDo + kTileBytes;
+  static constexpr int kOffStage = kOffDs + kDsBytes;    // two staging buffers
+  static constexpr int kOffStats = kOffStage + 2 * kStageBytes;  // lse[2][128], dpsum[128] floats
+  static constexpr int kOffBars = kOffStats + 3 * 512;
+  static constexpr int kSmemBytes = kOffBars + 256 + 1024;
+  static constexpr int kThreads = 448;
+  static constexpr int kTmemS = 0, kTmemDp = 128, kTmemDv = 256, kTmemDk = 256 + D;
+};
+
+__device__ __forceinline__ void cp_async_4(uint32_t smem_dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_dst), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ float4 ld_shared_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+
+template <int D>
+__global__ void __launch_bounds__(BwdConfig<D>::kThreads, 1)
+bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+           const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+           const __grid_constant__ CUtensorMap map_dq, const __grid_constant__ BwdParams p) {
+  using Cfg = BwdConfig<D>;
+  const Problem& pr = p.prob;
+  // ---- work item (uniform over the CTA; exits before any barrier or TMEM allocation)
+  int seq, n_block;
+  if (p.work_list) {
+    const int2 e = p.work_list[blockIdx.x];
+    seq = e.x;
+    n_block = e.y;
+    if (seq >= pr.batch) return;
+  } else {
+    seq = blockIdx.z;
+    n_block = blockIdx.x;
+  }
+  const int kv_head = blockIdx.y;
+  const SeqInfo s = seq_info(pr, seq);
+  const int n0 = n_block * kBlockN;
+  if (n0 >= s.lk) return;
+  const int c1 = imin(n0 + kBlockN, s.lk);
+  const int group = pr.heads_q / pr.heads_kv;
+  const int64_t stat_base = pr.cu_q ? 0 : (int64_t)seq * pr.seqlen_q;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t smem_k = base + Cfg::kOffK, smem_v = base + Cfg::kOffV, smem_q = base + Cfg::kOffQ;
+  const uint32_t smem_do = base + Cfg::kOffDo, smem_ds = base + Cfg::kOffDs, smem_stage = base + Cfg::kOffStage;
+  const uint32_t smem_lse = base + Cfg::kOffStats, smem_dpsum = smem_lse + 1024;
+  const uint32_t bars = base + Cfg::kOffBars;
+  const uint32_t bar_kv_full = bars, bar_q_full = bars + 8 /*[2]*/, bar_q_empty = bars + 24 /*[2]*/;
+  const uint32_t bar_do_full = bars + 40, bar_do_empty = bars + 48, bar_s_full = bars + 56, bar_p_full = bars + 64;
+  const uint32_t bar_dp_full = bars + 72, bar_ds_full = bars + 80, bar_dq_full = bars + 88, bar_dq_empty = bars + 96;
+  const uint32_t bar_final = bars + 104;
+  const uint32_t tmem_slot = bars + 112, abort_slot = bars + 116;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + (abort_slot - smem_u32(smem_raw)));
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+  const WaitCtx wctx{abort_flag, p.status};
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(bar_kv_full, 1);
+    mbar_init(bar_q_full, 33);
+    mbar_init(bar_q_full + 8, 33);
+    mbar_init(bar_q_empty, 1);
+    mbar_init(bar_q_empty + 8, 1);
+    mbar_init(bar_do_full, 33);
+    mbar_init(bar_do_empty, 1);
+    mbar_init(bar_s_full, 1);
+    mbar_init(bar_p_full, 256);
+    mbar_init(bar_dp_full, 1);
+    mbar_init(bar_ds_full, 256);
+    mbar_init(bar_dq_full, 1);
+    mbar_init(bar_dq_empty, 128);
+    mbar_init(bar_final, 1);
+    fence_barrier_init();
+  }
+  if (warp == 12) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  // Query blocks per head (the same for every head of the group).
+  int blocks_per_head = 0;
+  {
+    QueryCursor cur;
+    cur.init(&pr, seq, s, n0, c1);
+    OtherBlock qb;
+    while (cur.next(&qb)) ++blocks_per_head;
+  }
+  const int iterations = blocks_per_head * group;
+
+  if (warp == 13) {
+    // ------------------------------------------------------------------ loads
+    if (lane == 0) {
+      tma_prefetch_descriptor(&map_q);
+      tma_prefetch_descriptor(&map_do);
+      if (iterations > 0) {
+        mbar_expect_tx(bar_kv_full, 2 * Cfg::kTileBytes);
+#pragma unroll
+        for (int h = 0; h < Cfg::kHalves; ++h) {
+          tma_load_4d(smem_k + h * Cfg::kPanelBytes, &map_k, bar_kv_full, h * 64, kv_head, s.k0 + n0, s.batch_coord);
+          tma_load_4d(smem_v + h * Cfg::kPanelBytes, &map_v, bar_kv_full, h * 64, kv_head, s.k0 + n0, s.batch_coord);
+        }
+      }
+    }
+    int it = 0;
+    bool ok = true;
+    for (int g = 0; ok && g < group; ++g) {
+      const int head = kv_head * group + g;
+      const float* lse_head = p.lse_log2 + (int64_t)head * p.rows;
+      const float* dpsum_head = p.dpsum + (int64_t)head * p.rows;
+      QueryCursor cur;
+      cur.init(&pr, seq, s, n0, c1);
+      OtherBlock qb;
+      while (cur.next(&qb)) {
+        const int st = it & 1;
+        const int64_t row0 = stat_base + qb.row;
+        if (!mbar_wait_warp(bar_q_empty + 8 * st, ((it >> 1) & 1) ^ 1, wctx, kWaitBwdLoad)) { ok = false; break; }
+        if (lane == 0) {
+          mbar_expect_tx(bar_q_full + 8 * st, Cfg::kTileBytes);
+#pragma unroll
+          for (int h = 0; h < Cfg::kHalves; ++h)
+            tma_load_4d(smem_q + st * Cfg::kTileBytes + h * Cfg::kPanelBytes, &map_q, bar_q_full + 8 * st, h * 64, head,
+                        qb.row, s.batch_coord);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int r = lane + 32 * k;
+          if (row0 + r < p.rows) cp_async_4(smem_lse + st * 512 + r * 4, lse_head + row0 + r);
+        }
+        cp_async_arrive_noinc(bar_q_full + 8 * st);
+        if (!mbar_wait_warp(bar_do_empty, (it & 1) ^ 1, wctx, kWaitBwdLoad)) { ok = false; break; }
+        if (lane == 0) {
+          mbar_expect_tx(bar_do_full, Cfg::kTileBytes);
+#pragma unroll
+          for (int h = 0; h < Cfg::kHalves; ++h)
+            tma_load_4d(smem_do + h * Cfg::kPanelBytes, &map_do, bar_do_full, h * 64, head, qb.row, s.batch_coord);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int r = lane + 32 * k;
+          if (row0 + r < p.rows) cp_async_4(smem_dpsum + r * 4, dpsum_head + row0 + r);
+        }
+        cp_async_arrive_noinc(bar_do_full);
+        ++it;
+      }
+    }
+  } else if (warp == 12) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && iterations > 0) {
+      constexpr uint32_t idesc_st = umma_idesc_bf16(128, 128, 0, 0);   // S^T, dP^T
+      constexpr uint32_t idesc_dv = umma_idesc_bf16(128, D, 0, 1);     // dV: A in TMEM, B MN-major
+      constexpr uint32_t idesc_dk = umma_idesc_bf16(128, D, 0, 1);     // dK: A K-major smem, B MN-major
+      constexpr uint32_t idesc_dq = umma_idesc_bf16(128, D, 1, 1);     // dQ: A MN-major, B MN-major
+      const uint32_t t_s = tmem_base + Cfg::kTmemS, t_dp = tmem_base + Cfg::kTmemDp;
+      const uint32_t t_dv = tmem_base + Cfg::kTmemDv, t_dk = tmem_base + Cfg::kTmemDk;
+      auto mma_kmajor = [&](uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem) {  // D = A B^T over head_dim
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * Cfg::kPanelBytes + (kk & 3) * 32;
+          umma_ss(d_tmem, umma_smem_desc(a_smem + off, 16, 1024), umma_smem_desc(b_smem + off, 16, 1024), idesc_st, kk > 0);
+        }
+      };
+      bool ok = mbar_wait(bar_kv_full, 0, wctx, kWaitBwdMma) && mbar_wait(bar_q_full, 0, wctx, kWaitBwdMma);
+      if (ok) {
+        tc_fence_after();
+        mma_kmajor(t_s, smem_k, smem_q);
+        tc_commit(bar_s_full);
+        ok = mbar_wait(bar_do_full, 0, wctx, kWaitBwdMma);
+      }
+      if (ok) {
+        tc_fence_after();
+        mma_kmajor(t_dp, smem_v, smem_do);
+        tc_commit(bar_dp_full);
+      }
+      for (int it = 0; ok && it < iterations; ++it) {
+        const int st = it & 1;
+        const uint32_t q_tile = smem_q + st * Cfg::kTileBytes;
+        const bool more = it + 1 < iterations;
+        // dV += P^T dO
+        if (!mbar_wait(bar_p_full, it & 1, wctx, kWaitBwdMma)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ts(t_dv, t_s + (kk >> 2) * 64 + (kk & 3) * 8, umma_smem_desc(smem_do + kk * 2048, Cfg::kPanelBytes, 1024),
+                  idesc_dv, it > 0 || kk > 0);
+        tc_commit(bar_do_empty);
+        // S^T of the next iteration
+        if (more) {
+          if (!mbar_wait(bar_q_full + 8 * (st ^ 1), ((it + 1) >> 1) & 1, wctx, kWaitBwdMma)) { ok = false; break; }
+          tc_fence_after();
+          mma_kmajor(t_s, smem_k, smem_q + (st ^ 1) * Cfg::kTileBytes);
+          tc_commit(bar_s_full);
+        }
+        // dK += dS^T Q ; dQ = dS K
+        if (!mbar_wait(bar_ds_full, it & 1, wctx, kWaitBwdMma)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t a_off = (kk >> 2) * Cfg::kPanelBytes + (kk & 3) * 32;
+          umma_ss(t_dk, umma_smem_desc(smem_ds + a_off, 16, 1024), umma_smem_desc(q_tile + kk * 2048, Cfg::kPanelBytes, 1024),
+                  idesc_dk, it > 0 || kk > 0);
+        }
+        tc_commit(bar_q_empty + 8 * st);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ss(t_dp, umma_smem_desc(smem_ds + kk * 2048, Cfg::kPanelBytes, 1024),
+                  umma_smem_desc(smem_k + kk * 2048, Cfg::kPanelBytes, 1024), idesc_dq, kk > 0);
+        tc_commit(bar_dq_full);
+        // dP^T of the next iteration (its TMEM columns hold dQ until the reduce warps have drained it)
+        if (more) {
+          if (!mbar_wait(bar_do_full, (it + 1) & 1, wctx, kWaitBwdMma) ||
+              !mbar_wait(bar_dq_empty, it & 1, wctx, kWaitBwdMma)) { ok = false; break; }
+          tc_fence_after();
+          mma_kmajor(t_dp, smem_v, smem_do);
+          tc_commit(bar_dp_full);
+        }
+      }
+      if (ok) tc_commit(bar_final);
+    }
+  } else if (warp < 8) {
+    // ------------------------------------------------------------------ P and dS (thread = key row)
+    const int wg = warp >> 2;
+    const int r = (warp & 3) * 32 + lane;
+    const int cb = wg * 64;  // first query column of this group
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t t_s = tmem_base + lane_addr + Cfg::kTmemS, t_dp = tmem_base + lane_addr + Cfg::kTmemDp;
+    const int c = n0 + r;  // key column within its sequence
+    const bool key_valid = c < s.lk;
+    int left, right;
+    window_of(pr, seq, &left, &right);
+    const int off = s.lk - s.lq;
+    const uint32_t ds_row = smem_ds + wg * Cfg::kPanelBytes + r * 128;
+    int it = 0;
+    bool ok = true;
+    for (int g = 0; ok && g < group; ++g) {
+      QueryCursor cur;
+      cur.init(&pr, seq, s, n0, c1);
+      OtherBlock qb;
+      while (cur.next(&qb)) {
+        const int st = it & 1;
+        int qlo = 0, qhi = qb.limit - qb.col0;
+        if (qb.banded) {
+          if (right >= 0) qlo = imax(0, c - off - right - qb.col0);
+          if (left >= 0) qhi = imin(qhi, c - off + left + 1 - qb.col0);
+        }
+        if (!key_valid) qhi = 0;
+        const bool masked = __any_sync(0xffffffffu, qlo > cb || qhi < cb + 64);
+        // ---- P^T
+        if (!mbar_wait_warp(bar_s_full, it & 1, wctx, kWaitBwdCompute)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t pk[32];
+        {
+          float sc[64];
+          tmem_ld32(t_s + cb, reinterpret_cast<uint32_t*>(sc));
+          tmem_ld32(t_s + cb + 32, reinterpret_cast<uint32_t*>(sc) + 32);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float4 l4 = ld_shared_f4(smem_lse + st * 512 + (cb + 4 * j) * 4);
+            float p0 = ex2_approx(fmaf(sc[4 * j + 0], p.scale_log2, -l4.x));
+            float p1 = ex2_approx(fmaf(sc[4 * j + 1], p.scale_log2, -l4.y));
+            float p2 = ex2_approx(fmaf(sc[4 * j + 2], p.scale_log2, -l4.z));
+            float p3 = ex2_approx(fmaf(sc[4 * j + 3], p.scale_log2, -l4.w));
+            if (masked) {
+              const int q = cb + 4 * j;
+              p0 = (q + 0 >= qlo && q + 0 < qhi) ? p0 : 0.f;
+              p1 = (q + 1 >= qlo && q + 1 < qhi) ? p1 : 0.f;
+              p2 = (q + 2 >= qlo && q + 2 < qhi) ? p2 : 0.f;
+              p3 = (q + 3 >= qlo && q + 3 < qhi) ? p3 : 0.f;
+            }
+            pk[2 * j] = pack_bf16x2(p0, p1);
+            pk[2 * j + 1] = pack_bf16x2(p2, p3);
+          }
+        }
+        // P^T of a group goes over the first 32 columns of the group's own S^T columns.
+        tmem_st16(t_s + cb, pk);
+        tmem_st16(t_s + cb + 16, pk + 16);
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_p_full);
+        // ---- dS^T
+        if (!mbar_wait_warp(bar_dp_full, it & 1, wctx, kWaitBwdCompute)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t dsk[32];
+        {
+          float dp[64];
+          tmem_ld32(t_dp + cb, reinterpret_cast<uint32_t*>(dp));
+          tmem_ld32(t_dp + cb + 32, reinterpret_cast<uint32_t*>(dp) + 32);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float4 d4 = ld_shared_f4(smem_dpsum + (cb + 4 * j) * 4);
+            const float p0 = __uint_as_float(pk[2 * j] << 16), p1 = __uint_as_float(pk[2 * j] & 0xffff0000u);
+            const float p2 = __uint_as_float(pk[2 * j + 1] << 16), p3 = __uint_as_float(pk[2 * j + 1] & 0xffff0000u);
+            float s0 = p0 * (dp[4 * j + 0] - d4.x), s1 = p1 * (dp[4 * j + 1] - d4.y);
+            float s2 = p2 * (dp[4 * j + 2] - d4.z), s3 = p3 * (dp[4 * j + 3] - d4.w);
+            if (masked) {
+              const int q = cb + 4 * j;
+              s0 = (q + 0 >= qlo && q + 0 < qhi) ? s0 : 0.f;
+              s1 = (q + 1 >= qlo && q + 1 < qhi) ? s1 : 0.f;
+              s2 = (q + 2 >= qlo && q + 2 < qhi) ? s2 : 0.f;
+              s3 = (q + 3 >= qlo && q + 3 < qhi) ? s3 : 0.f;
+            }
+            dsk[2 * j] = pack_bf16x2(s0, s1);
+            dsk[2 * j + 1] = pack_bf16x2(s2, s3);
+          }
+        }
+        tc_fence_before();
+        // The dS tile of the previous iteration must have been consumed by its dK and dQ MMAs.
+        if (it > 0 && !mbar_wait_warp(bar_dq_full, (it - 1) & 1, wctx, kWaitBwdCompute)) { ok = false; break; }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          st_shared_v4(ds_row + ((j ^ (r & 7)) << 4), dsk[4 * j], dsk[4 * j + 1], dsk[4 * j + 2], dsk[4 * j + 3]);
+        fence_proxy_async_smem();
+        mbar_arrive(bar_ds_full);
+        ++it;
+      }
+    }
+    // ---- epilogue: group 0 writes dV, group 1 writes dK * scale
+    if (ok) {
+      const bool have = iterations > 0;
+      if (have) ok = mbar_wait_warp(bar_final, 0, wctx, kWaitEpilogue);
+      if (ok) {
+        tc_fence_after();
+        __nv_bfloat16* out = wg == 0 ? p.dv : p.dk;
+        const int64_t bs = wg == 0 ? p.dv_batch_stride : p.dk_batch_stride;
+        const int64_t rs = wg == 0 ? p.dv_row_stride : p.dk_row_stride;
+        const int64_t hs = wg == 0 ? p.dv_head_stride : p.dk_head_stride;
+        const float mul = wg == 0 ? 1.f : p.scale;
+        const uint32_t t_acc = tmem_base + lane_addr + (wg == 0 ? Cfg::kTmemDv : Cfg::kTmemDk);
+        uint4* dst = reinterpret_cast<uint4*>(out + s.batch_coord * bs + (int64_t)(s.k0 + c) * rs + (int64_t)kv_head * hs);
+#pragma unroll
+        for (int ch = 0; ch < D / 32; ++ch) {
+          uint32_t acc[32];
+          if (have) {
+            tmem_ld32(t_acc + 32 * ch, acc);
+            tc_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[i] = 0;
+          }
+          if (key_valid) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(acc[8 * i + 0]) * mul, __uint_as_float(acc[8 * i + 1]) * mul);
+              v.y = pack_bf16x2(__uint_as_float(acc[8 * i + 2]) * mul, __uint_as_float(acc[8 * i + 3]) * mul);
+              v.z = pack_bf16x2(__uint_as_float(acc[8 * i + 4]) * mul, __uint_as_float(acc[8 * i + 5]) * mul);
+              v.w = pack_bf16x2(__uint_as_float(acc[8 * i + 6]) * mul, __uint_as_float(acc[8 * i + 7]) * mul);
+              dst[4 * ch + i] = v;
+            }
+          }
+        }
+        tc_fence_before();
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ dQ drain (warps 8-11, thread = query row)
+    const int r = (warp & 3) * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t t_dq = tmem_base + lane_addr + Cfg::kTmemDp;
+    const bool leader = threadIdx.x == 8 * 32;
+    int it = 0;
+    uint32_t chunks = 0;
+    bool ok = true;
+    for (int g = 0; ok && g < group; ++g) {
+      const int head = kv_head * group + g;
+      QueryCursor cur;
+      cur.init(&pr, seq, s, n0, c1);
+      OtherBlock qb;
+      while (cur.next(&qb)) {
+        const int row0 = (int)(stat_base + qb.row);
+        if (!mbar_wait_warp(bar_dq_full, it & 1, wctx, kWaitBwdReduce)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int ch = 0; ch < D / 32; ++ch) {
+          uint32_t acc[32];
+          tmem_ld32(t_dq + 32 * ch, acc);
+          tc_wait_ld();
+          if (ch == D / 32 - 1) {
+            tc_fence_before();
+            mbar_arrive(bar_dq_empty);
+          }
+          const uint32_t stage = smem_stage + (chunks & 1) * Cfg::kStageBytes;
+          if (leader) bulk_wait_group_read<1>();  // the copy that read this buffer two chunks ago is done with it
+          named_barrier_sync(1, 128);
+          const uint32_t row_addr = stage + r * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            st_shared_v4(row_addr + ((j ^ (r & 7)) << 4), acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+          fence_proxy_async_smem();
+          named_barrier_sync(1, 128);
+          if (leader) {
+            tma_reduce_add_4d(&map_dq, stage, 32 * ch, head, row0, 0);
+            bulk_commit_group();
+          }
+          ++chunks;
+        }
+        ++it;
+      }
+    }
+    if (leader) bulk_wait_group<0>();
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (*abort_flag) {
+    for (int i = 0; i < 50; ++i) __nanosleep(20000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 12) tmem_dealloc(tmem_base, 512);
+}
+
+// ---------------------------------------------------------------------------------------------- pre / post process
+struct RowMap {
+  const int32_t* cu_q;  // null = fixed length
+  int batch, seqlen_q;
+  int64_t rows;  // batch * seqlen_q or total_q
+};
+// Maps a statistics row to (sequence, row within the sequence, batch coordinate, packed row).
+__device__ __forceinline__ bool locate_row(const RowMap& m, int64_t row, int* batch_coord, int64_t* tensor_row) {
+  if (m.cu_q) {
+    if (row >= m.cu_q[m.batch]) return false;  // rows past the last sequence stay untouched
+    *batch_coord = 0;
+    *tensor_row = row;
+  } else {
+    *batch_coord = (int)(row / m.seqlen_q);
+    *tensor_row = row - (int64_t)(*batch_coord) * m.seqlen_q;
+  }
+  return true;
+}
+
+// One warp per (row, head): dpsum = sum_d O dO, lse_log2 = lse log2(e) (+inf when lse = -inf), dq_accum row = 0.
+template <int D>
+__global__ void __launch_bounds__(256) bwd_preprocess_kernel(
+    const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout, const float* __restrict__ lse,
+    int64_t o_bs, int64_t o_rs, int64_t o_hs, int64_t do_bs, int64_t do_rs, int64_t do_hs, int64_t lse_bs, int64_t lse_hs,
+    RowMap map, int heads, float* __restrict__ lse_log2, float* __restrict__ dpsum, float* __restrict__ dq_accum) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int head = blockIdx.y;
+  if (row >= map.rows) return;
+  int batch_coord;
+  int64_t tensor_row;
+  if (!locate_row(map, row, &batch_coord, &tensor_row)) return;
+  constexpr int kPerLane = D / 32;  // 2 or 4 BF16 values
+  const __nv_bfloat16* o_ptr = o + batch_coord * o_bs + tensor_row * o_rs + (int64_t)head * o_hs + lane * kPerLane;
+  const __nv_bfloat16* do_ptr = dout + batch_coord * do_bs + tensor_row * do_rs + (int64_t)head * do_hs + lane * kPerLane;
+  float sum = 0.f;
+  if constexpr (kPerLane == 4) {
+    const uint2 a = *reinterpret_cast<const uint2*>(o_ptr), b = *reinterpret_cast<const uint2*>(do_ptr);
+    sum = __uint_as_float(a.x << 16) * __uint_as_float(b.x << 16) +
+          __uint_as_float(a.x & 0xffff0000u) * __uint_as_float(b.x & 0xffff0000u) +
+          __uint_as_float(a.y << 16) * __uint_as_float(b.y << 16) +
+          __uint_as_float(a.y & 0xffff0000u) * __uint_as_float(b.y & 0xffff0000u);
+  } else {
+    const uint32_t a = *reinterpret_cast<const uint32_t*>(o_ptr), b = *reinterpret_cast<const uint32_t*>(do_ptr);
+    sum = __uint_as_float(a << 16) * __uint_as_float(b << 16) +
+          __uint_as_float(a & 0xffff0000u) * __uint_as_float(b & 0xffff0000u);
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+  const int64_t stat = (int64_t)head * map.rows + row;
+  if (lane == 0) {
+    const float value = lse[batch_coord * lse_bs + (int64_t)head * lse_hs + tensor_row];
+    lse_log2[stat] = value == -INFINITY ? INFINITY : value * kLog2e;
+    dpsum[stat] = sum;
+  }
+  float* acc = dq_accum + stat * D + lane * kPerLane;
+  if constexpr (kPerLane == 4) {
+    *reinterpret_cast<float4*>(acc) = make_float4(0.f, 0.f, 0.f, 0.f);
+  } else {
+    *reinterpret_cast<float2*>(acc) = make_float2(0.f, 0.f);
+  }
+}
+
+// dq = bf16(scale * dq_accum) for valid rows.
+template <int D>
+__global__ void __launch_bounds__(256) bwd_postprocess_kernel(const float* __restrict__ dq_accum, RowMap map, float scale,
+                                                              __nv_bfloat16* __restrict__ dq, int64_t dq_bs,
+                                                              int64_t dq_rs, int64_t dq_hs) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int head = blockIdx.y;
+  if (row >= map.rows) return;
+  int batch_coord;
+  int64_t tensor_row;
+  if (!locate_row(map, row, &batch_coord, &tensor_row)) return;
+  constexpr int kPerLane = D / 32;
+  const float* acc = dq_accum + ((int64_t)head * map.rows + row) * D + lane * kPerLane;
+  __nv_bfloat16* out = dq + batch_coord * dq_bs + tensor_row * dq_rs + (int64_t)head * dq_hs + lane * kPerLane;
+  if constexpr (kPerLane == 4) {
+    const float4 v = *reinterpret_cast<const float4*>(acc);
+    uint2 packed;
+    packed.x = pack_bf16x2(v.x * scale, v.y * scale);
+    packed.y = pack_bf16x2(v.z * scale, v.w * scale);
+    *reinterpret_cast<uint2*>(out) = packed;
+  } else {
+    const float2 v = *reinterpret_cast<const float2*>(acc);
+    *reinterpret_cast<uint32_t*>(out) = pack_bf16x2(v.x * scale, v.y * scale);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- host side
+struct BwdWorkspace {
+  size_t lse_log2, dpsum, dq_accum, work_list, total;
+  int64_t rows, entries;
+};
+
+static BwdWorkspace plan_workspace(const b200fa_problem& p) {
+  BwdWorkspace w;
+  const bool packed = p.cu_seqlens_q != nullptr;
+  w.rows = packed ? (int64_t)p.seqlen_q : (int64_t)p.batch * p.seqlen_q;
+  const size_t stat_bytes = ((size_t)p.heads_q * w.rows * 4 + 255) & ~size_t(255);
+  w.lse_log2 = 0;
+  w.dpsum = stat_bytes;
+  w.dq_accum = 2 * stat_bytes;
+  const size_t acc_bytes = ((size_t)p.heads_q * w.rows * p.head_dim * 4 + 255) & ~size_t(255);
+  w.work_list = w.dq_accum + acc_bytes;
+  w.entries = packed ? work_list_entries(p.seqlen_k, p.batch, kBlockN) : 0;
+  w.total = w.work_list + (size_t)w.entries * 8;
+  return w;
+}
+
+size_t bwd_workspace_bytes(const b200fa_problem& p) { return plan_workspace(p).total; }
+
+template <int D>
+static int launch_main(const b200fa_bwd_args& a, const BwdParams& p, dim3 grid, float* dq_accum, int64_t stat_rows,
+                       cudaStream_t stream) {
+  using Cfg = BwdConfig<D>;
+  const b200fa_problem& bp = a.problem;
+  const bool packed = bp.cu_seqlens_q != nullptr;
+  const int64_t rows_q = bp.seqlen_q, rows_k = bp.seqlen_k;
+  const int64_t tensor_batch = packed ? 1 : bp.batch;
+  // A problem without query rows has nothing to load; its dK and dV are zero.
+  const bool no_queries = rows_q == 0 || stat_rows == 0;
+  CUtensorMap map_q, map_k, map_v, map_do, map_dq;
+  int status;
+  const void* q_base = no_queries ? a.k : a.q;
+  const void* do_base = no_queries ? a.k : a.dout;
+  const int64_t q_rows = no_queries ? 1 : rows_q;
+  const int64_t qh = no_queries ? 1 : bp.heads_q;
+  status = encode_tensor_map(&map_q, q_base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, qh, q_rows, tensor_batch,
+                             no_queries ? D : a.q_stride[2], no_queries ? D : a.q_stride[1],
+                             no_queries ? D : (packed ? q_rows * a.q_stride[1] : a.q_stride[0]), 64, kBlockM);
+  if (status != B200FA_OK) return status;
+  status = encode_tensor_map(&map_do, do_base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, qh, q_rows, tensor_batch,
+                             no_queries ? D : a.dout_stride[2], no_queries ? D : a.dout_stride[1],
+                             no_queries ? D : (packed ? q_rows * a.dout_stride[1] : a.dout_stride[0]), 64, kBlockM);
+  if (status != B200FA_OK) return status;
+  status = encode_tensor_map(&map_k, a.k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, bp.heads_kv, rows_k, tensor_batch,
+                             a.k_stride[2], a.k_stride[1], packed ? rows_k * a.k_stride[1] : a.k_stride[0], 64, kBlockN);
+  if (status != B200FA_OK) return status;
+  status = encode_tensor_map(&map_v, a.v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, bp.heads_kv, rows_k, tensor_batch,
+                             a.v_stride[2], a.v_stride[1], packed ? rows_k * a.v_stride[1] : a.v_stride[0], 64, kBlockN);
+  if (status != B200FA_OK) return status;
+  if (no_queries) {
+    map_dq = map_q;
+  } else {
+    status = encode_tensor_map(&map_dq, dq_accum, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, D, bp.heads_q, stat_rows, 1,
+                               stat_rows * D, D, (int64_t)bp.heads_q * stat_rows * D, 32, kBlockM);
+    if (status != B200FA_OK) return status;
+  }
+
+  static bool attribute_set = false;
+  if (!attribute_set) {
+    B200FA_CUDA_CHECK(cudaFuncSetAttribute(bwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    attribute_set = true;
+  }
+  bwd_kernel<D><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_q, map_k, map_v, map_do, map_dq, p);
+  B200FA_CUDA_CHECK(cudaGetLastError());
+
+  return B200FA_OK;
+}
+
+template <int D>
+static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
+  using Cfg = BwdConfig<D>;
+  const b200fa_problem& bp = a.problem;
+  const bool packed = bp.cu_seqlens_q != nullptr;
+  const BwdWorkspace w = plan_workspace(bp);
+  B200FA_REQUIRE(a.workspace_bytes >= w.total && (w.total == 0 || a.workspace), "backward workspace is too small: need %zu bytes",
+                 w.total);
+  B200FA_REQUIRE(reinterpret_cast<uintptr_t>(a.workspace) % 256 == 0, "backward workspace must be 256-byte aligned");
+  const int64_t rows_q = bp.seqlen_q, rows_k = bp.seqlen_k;
+  if (bp.batch == 0) return B200FA_OK;
+  const bool no_keys = rows_k == 0;
+  uint8_t* ws = static_cast<uint8_t*>(a.workspace);
+  float* lse_log2 = reinterpret_cast<float*>(ws + w.lse_log2);
+  float* dpsum = reinterpret_cast<float*>(ws + w.dpsum);
+  float* dq_accum = reinterpret_cast<float*>(ws + w.dq_accum);
+  const int64_t tensor_batch = packed ? 1 : bp.batch;
+
+  RowMap map{bp.cu_seqlens_q, bp.batch, bp.seqlen_q, w.rows};
+  if (w.rows > 0) {
+    dim3 grid((unsigned)((w.rows + 7) / 8), (unsigned)bp.heads_q);
+    bwd_preprocess_kernel<D><<<grid, 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(a.out), static_cast<const __nv_bfloat16*>(a.dout), a.softmax_lse,
+        packed ? 0 : a.out_stride[0], a.out_stride[1], a.out_stride[2], packed ? 0 : a.dout_stride[0], a.dout_stride[1],
+        a.dout_stride[2], packed ? 0 : a.lse_stride[0], a.lse_stride[1], map, bp.heads_q, lse_log2, dpsum, dq_accum);
+    B200FA_CUDA_CHECK(cudaGetLastError());
+  }
+
+  BwdParams p;
+  p.prob = to_problem(bp);
+  p.scale = bp.softmax_scale;
+  p.scale_log2 = bp.softmax_scale * kLog2e;
+  p.lse_log2 = lse_log2;
+  p.dpsum = dpsum;
+  p.rows = w.rows;
+  p.dk = static_cast<__nv_bfloat16*>(a.dk);
+  p.dv = static_cast<__nv_bfloat16*>(a.dv);
+  p.dk_batch_stride = packed ? 0 : a.dk_stride[0];
+  p.dk_row_stride = a.dk_stride[1];
+  p.dk_head_stride = a.dk_stride[2];
+  p.dv_batch_stride = packed ? 0 : a.dv_stride[0];
+  p.dv_row_stride = a.dv_stride[1];
+  p.dv_head_stride = a.dv_stride[2];
+  p.work_list = nullptr;
+  p.status = device_status_word();
+  if (!p.status) return B200FA_ERR_CUDA;
+
+  dim3 grid;
+  bool run_main = !no_keys;
+  if (packed) {
+    if (w.entries == 0) run_main = false;
+  }
+  if (run_main && packed) {
+    const int32_t* other = bp.cu_visible_q ? bp.cu_visible_q : bp.cu_seqlens_q;
+    int status = b200fa_work_list(bp.cu_seqlens_k, other, bp.batch, kBlockN, 0, (int32_t)w.entries,
+                                  reinterpret_cast<int32_t*>(ws + w.work_list), stream);
+    if (status != B200FA_OK) return status;
+    p.work_list = reinterpret_cast<const int2*>(ws + w.work_list);
+    grid = dim3((unsigned)w.entries, (unsigned)bp.heads_kv, 1);
+  } else if (run_main) {
+    grid = dim3((unsigned)ceil_div(bp.seqlen_k, kBlockN), (unsigned)bp.heads_kv, (unsigned)bp.batch);
+  }
+  if (run_main) {
+    int status = launch_main<D>(a, p, grid, dq_accum, w.rows, stream);
+    if (status != B200FA_OK) return status;
+  }
+
+  if (w.rows > 0) {
+    dim3 post((unsigned)((w.rows + 7) / 8), (unsigned)bp.heads_q);
+    bwd_postprocess_kernel<D><<<post, 256, 0, stream>>>(dq_accum, map, bp.softmax_scale, static_cast<__nv_bfloat16*>(a.dq),
+                                                        packed ? 0 : a.dq_stride[0], a.dq_stride[1], a.dq_stride[2]);
+    B200FA_CUDA_CHECK(cudaGetLastError());
+  }
+  return B200FA_OK;
+}
+
+int launch_bwd(const b200fa_bwd_args& a, cudaStream_t stream) {
+  switch (a.problem.head_dim) {
+    case 64:
+      return launch_bwd_d<64>(a, stream);
+    case 128:
+      return launch_bwd_d<128>(a, stream);
+    default:
+      set_error("head_dim %d is not supported by the backward kernels (supported: 64, 128)", a.problem.head_dim);
+      return B200FA_ERR_UNSUPPORTED;
+  }
+}
+
 }  // namespace b200fa

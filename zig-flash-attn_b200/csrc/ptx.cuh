@@ -79,7 +79,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Bounded wait on the phase with the given parity.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, WaitCtx ctx, int code) {
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, WaitCtx ctx, int code) {
   const unsigned long long start = global_timer_ns();
   for (;;) {
 #pragma unroll 1
