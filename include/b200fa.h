@@ -98,6 +98,11 @@ size_t b200fa_bwd_workspace_bytes(const b200fa_problem* problem);
  * postprocess. dQ accumulates with floating-point atomics (not deterministic), as in the reference. */
 int b200fa_bwd(const b200fa_bwd_args* args, void* stream);
 
+/* Measurement hook (no counterpart in the reference): the next b200fa_bwd call of the calling thread records the four
+ * cudaEvent_t handles events[0..3] on its stream -- before the preprocess kernel, before the main kernel, after the
+ * main kernel, after the postprocess kernel -- so a benchmark can time the main kernel by itself. NULL clears it. */
+int b200fa_bwd_timing_events(void* const* events);
+
 /* Replaces inter_sequence.prepare_metadata (reference src/zigfa/_impl/inter_sequence.py:223-254).
  * Outputs: bits_t (n, ceil(n/32)) int32, cu_visible_k (n + 1) int32, cu_visible_q (n + 1) int32 (saturating). */
 int b200fa_interseq_metadata(const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, const int32_t* visibility_bits,

@@ -1,0 +1,303 @@
+"""GPU parity tests of the attention kernels through the public API (which calls the C ABI): fixed length, packed
+(varlen) and the packed-argument variants, forward and backward, against the oracle with the stated tolerance.
+Shapes follow the families the reference tests (reference tests/shapes.py:11-42, tests/test_backward.py,
+tests/test_torch.py)."""
+import itertools
+
+import pytest
+import torch
+
+import attention_oracle as oracle
+import parity
+import zigfa
+from zigfa._impl import ops
+
+pytestmark = pytest.mark.gpu
+
+HEAD_LAYOUTS = {"mha": (6, 6), "mqa": (6, 1), "gqa": (6, 3)}
+HEAD_DIMS = (64, 128)
+SEQLENS = [
+    (1, 1), (3, 3), (64, 32), (64, 128), (128, 128), (128, 192), (256, 256), (239, 1), (799, 3), (113, 203),
+    (113, 128), (128, 217), (113, 211), (108, 256), (256, 512), (384, 256), (640, 128), (1024, 1024), (1023, 1024),
+    (1024, 1023), (2048, 2048),
+]
+WINDOW_KINDS = ["dense", "causal", "local", "local_left", "local_right"]
+
+
+def window_of(kind, seqlen_k):
+    generator = torch.Generator().manual_seed(seqlen_k)
+    left, right = torch.randint(0, seqlen_k, (2,), generator=generator).tolist()
+    return {
+        "dense": ((-1, -1), False),
+        "causal": ((-1, 0), True),
+        "local": ((left, right), False),
+        "local_left": ((left, -1), False),
+        "local_right": ((-1, right), False),
+    }[kind]
+
+
+def randn(*shape, requires_grad=False):
+    return torch.randn(*shape, device="cuda", dtype=torch.bfloat16).requires_grad_(requires_grad)
+
+
+def run_fixed(q, k, v, dout, **options):
+    out, lse = zigfa.flash_attn_func(q, k, v, return_attn_probs=True, **options)
+    grads = torch.autograd.grad(out, (q, k, v), dout) if dout is not None else None
+    return out.detach(), lse, grads
+
+
+@pytest.mark.parametrize("head_dim", HEAD_DIMS)
+@pytest.mark.parametrize("kind", WINDOW_KINDS)
+def test_fixed_length_matches_oracle(head_dim, kind):
+    for (seqlen_q, seqlen_k), heads_name in itertools.product(SEQLENS, HEAD_LAYOUTS):
+        heads_q, heads_kv = HEAD_LAYOUTS[heads_name]
+        window, causal = window_of(kind, seqlen_k)
+        torch.manual_seed(seqlen_q * 31 + seqlen_k)
+        batch = 2 if seqlen_q <= 1024 else 1
+        q, k, v = randn(batch, seqlen_q, heads_q, head_dim, requires_grad=True), randn(batch, seqlen_k, heads_kv, head_dim, requires_grad=True), randn(batch, seqlen_k, heads_kv, head_dim, requires_grad=True)
+        dout = randn(batch, seqlen_q, heads_q, head_dim)
+        results = run_fixed(q, k, v, dout, causal=causal, window_size=window)
+        parity.check_fixed(results, q.detach(), k.detach(), v.detach(), dout, causal, window,
+                           notes=f"[{kind} {seqlen_q}x{seqlen_k} {heads_name} d{head_dim}]")
+
+
+def test_large_gqa_groups_and_long_sequences():
+    for batch, heads_q, heads_kv, seqlen in [(3, 18, 6, 4096), (8, 16, 2, 2048), (1, 8, 2, 4096), (1, 32, 1, 1024)]:
+        torch.manual_seed(seqlen + heads_q)
+        q, k, v = randn(batch, seqlen, heads_q, 128, requires_grad=True), randn(batch, seqlen, heads_kv, 128, requires_grad=True), randn(batch, seqlen, heads_kv, 128, requires_grad=True)
+        dout = randn(batch, seqlen, heads_q, 128)
+        results = run_fixed(q, k, v, dout, causal=True)
+        parity.check_fixed(results, q.detach(), k.detach(), v.detach(), dout, True, (-1, -1), notes=f"[gqa {heads_q}/{heads_kv} s{seqlen}]")
+
+
+@pytest.mark.parametrize("window", [(0, 0), (63, 0), (0, 63), (127, 128)])
+def test_narrow_windows(window):
+    for seqlen in (1024, 2048, 4096):
+        torch.manual_seed(seqlen)
+        q, k, v = randn(1, seqlen, 4, 128, requires_grad=True), randn(1, seqlen, 2, 128, requires_grad=True), randn(1, seqlen, 2, 128, requires_grad=True)
+        dout = randn(1, seqlen, 4, 128)
+        results = run_fixed(q, k, v, dout, window_size=window)
+        parity.check_fixed(results, q.detach(), k.detach(), v.detach(), dout, False, window, notes=f"[window {window} s{seqlen}]")
+    if window == (0, 0):
+        # a zero window sees only the diagonal: out == v (reference tests/test_reference.py:74-80)
+        q, k, v = randn(2, 300, 4, 64), randn(2, 300, 4, 64), randn(2, 300, 4, 64)
+        out = zigfa.flash_attn_func(q, k, v, window_size=(0, 0))
+        assert torch.equal(out, v)
+
+
+def test_rows_without_keys_are_zero():
+    # causal with more queries than keys: the first seqlen_q - seqlen_k rows see nothing
+    q, k, v = randn(2, 300, 4, 128, requires_grad=True), randn(2, 40, 2, 128, requires_grad=True), randn(2, 40, 2, 128, requires_grad=True)
+    out, lse = zigfa.flash_attn_func(q, k, v, causal=True, return_attn_probs=True)
+    assert (out[:, :260] == 0).all() and (lse[:, :, :260] == float("-inf")).all()
+    assert torch.isfinite(lse[:, :, 260:]).all()
+    dq, dk, dv = torch.autograd.grad(out, (q, k, v), torch.randn_like(out))
+    assert (dq[:, :260] == 0).all()
+    assert not torch.isnan(dk).any() and not torch.isnan(dv).any()
+
+
+def test_softmax_scale_and_ignored_options():
+    q, k, v = randn(2, 256, 4, 64), randn(2, 256, 2, 64), randn(2, 256, 2, 64)
+    base = zigfa.flash_attn_func(q, k, v, causal=True)
+    for options in (dict(pack_gqa=True), dict(pack_gqa=False), dict(sm_margin=8), dict(num_splits=0)):
+        assert torch.equal(zigfa.flash_attn_func(q, k, v, causal=True, **options), base)
+    # causal ignores the right bound of window_size (reference src/zigfa/_impl/ops.py:383)
+    assert torch.equal(zigfa.flash_attn_func(q, k, v, causal=True, window_size=(-1, 17)), base)
+    scaled = zigfa.flash_attn_func(q, k, v, causal=True, softmax_scale=0.3)
+    reference, _ = oracle.attention(q, k, v, causal=True, softmax_scale=0.3)
+    assert (scaled.float() - reference).abs().max() < 3e-2
+
+
+# ------------------------------------------------------------------------------------------------ packed (varlen)
+def cu_seqlens(lengths):
+    return torch.tensor([0, *itertools.accumulate(lengths)], dtype=torch.int32, device="cuda")
+
+
+def run_varlen(q, k, v, dout, cu_q, cu_k, max_q, max_k, **options):
+    out, lse = zigfa.flash_attn_varlen_func(q, k, v, cu_q, cu_k, max_q, max_k, return_attn_probs=True, **options)
+    grads = torch.autograd.grad(out, (q, k, v), dout) if dout is not None else None
+    return out.detach(), lse, grads
+
+
+def varlen_lengths(batch, max_q, max_k, generator, zero_lengths):
+    lengths_q = torch.randint(max(1, max_q - 20), max_q + 1, (batch,), generator=generator)
+    lengths_k = torch.randint(max(1, max_k - 20), max_k + 1, (batch,), generator=generator)
+    if zero_lengths:
+        lengths_k[::5] = 0
+        lengths_q[2::7] = 0
+    return lengths_q.tolist(), lengths_k.tolist()
+
+
+VARLEN_SEQLENS = [(1, 1), (1, 3), (2, 1), (511, 1), (3, 513), (64, 128), (128, 128), (113, 203), (108, 256), (256, 512),
+                  (640, 128), (1024, 1023)]
+
+
+@pytest.mark.parametrize("kind", ["dense", "causal", "local"])
+@pytest.mark.parametrize("zero_lengths", [False, True])
+def test_varlen_matches_oracle(kind, zero_lengths):
+    for index, (max_q, max_k) in enumerate(VARLEN_SEQLENS):
+        head_dim = HEAD_DIMS[index % 2]
+        heads_q, heads_kv = list(HEAD_LAYOUTS.values())[index % 3]
+        batch = 49 if max_q * max_k <= 64 * 128 else 7
+        generator = torch.Generator().manual_seed(index)
+        lengths_q, lengths_k = varlen_lengths(batch, max_q, max_k, generator, zero_lengths)
+        padding = [1, 37, 128][index % 3]  # rows past the last boundary must stay untouched
+        window, causal = window_of(kind, max_k)
+        torch.manual_seed(index)
+        q = randn(sum(lengths_q) + padding, heads_q, head_dim, requires_grad=True)
+        k, v = (randn(sum(lengths_k) + padding, heads_kv, head_dim, requires_grad=True) for _ in range(2))
+        dout = randn(*q.shape)
+        cu_q, cu_k = cu_seqlens(lengths_q), cu_seqlens(lengths_k)
+        results = run_varlen(q, k, v, dout, cu_q, cu_k, max_q, max_k, causal=causal, window_size=window)
+        mask = oracle.packed_mask(cu_q.tolist(), cu_k.tolist(), (window[0], 0) if causal else window)
+        flash = parity.aten_flash(q.detach(), k.detach(), v.detach(), dout, cu_q, cu_k, max(max(lengths_q), 1),
+                                  max(max(lengths_k), 1), (window[0], 0) if causal else window, head_dim**-0.5)
+        parity.check_masked(results, q.detach(), k.detach(), v.detach(), dout, mask, flash=flash,
+                            notes=f"[varlen {kind} {max_q}x{max_k} zero={zero_lengths}]")
+
+
+def test_varlen_leaves_rows_past_the_last_sequence_untouched():
+    lengths = [100, 0, 300, 77]
+    total, padding = sum(lengths), 64
+    q, k, v = (randn(total + padding, 4, 128) for _ in range(3))
+    cu = cu_seqlens(lengths)
+    out = torch.full_like(q, float("nan"))
+    lse = torch.full((4, total + padding), float("nan"), device="cuda")
+    ops.launch_forward(q, k, v, out, lse, cu, cu, 128**-0.5, -1, 0)
+    assert torch.isnan(out[total:]).all() and torch.isnan(lse[:, total:]).all()
+    assert not torch.isnan(out[:total]).any() and not torch.isnan(lse[:, :total]).any()
+    dout = randn(*q.shape)
+    dq, dk, dv = (torch.full_like(x, float("nan")) for x in (q, k, v))
+    ops.launch_backward(dout, q, k, v, out, lse, dq, dk, dv, cu, cu, 128**-0.5, -1, 0)
+    for gradient in (dq, dk, dv):
+        assert torch.isnan(gradient[total:]).all() and not torch.isnan(gradient[:total]).any()
+
+
+def test_varlen_equals_fixed_length_per_sequence():
+    lengths = [512, 256, 1024]
+    q, k, v = (randn(sum(lengths), 8, 128) for _ in range(3))
+    cu = cu_seqlens(lengths)
+    out = zigfa.flash_attn_varlen_func(q, k, v, cu, cu, 1024, 1024, causal=True)
+    start = 0
+    for length in lengths:
+        piece = slice(start, start + length)
+        single = zigfa.flash_attn_func(q[None, piece], k[None, piece], v[None, piece], causal=True)[0]
+        assert torch.equal(out[piece], single)
+        start += length
+
+
+# ------------------------------------------------------------------------------------------------ packed arguments
+def test_qkvpacked_and_kvpacked_variants():
+    torch.manual_seed(3)
+    batch, seqlen, heads_q, heads_kv, d = 2, 320, 6, 2, 128
+    qkv5 = randn(batch, seqlen, 3, heads_q, d, requires_grad=True)
+    out5 = zigfa.flash_attn_qkvpacked_func(qkv5, causal=True)
+    dout = randn(*out5.shape)
+    (dqkv5,) = torch.autograd.grad(out5, qkv5, dout)
+    q, k, v = (x.detach().clone().requires_grad_() for x in qkv5.unbind(2))
+    out = zigfa.flash_attn_func(q, k, v, causal=True)
+    dq, dk, dv = torch.autograd.grad(out, (q, k, v), dout)
+    assert torch.equal(out5, out) and dqkv5.shape == qkv5.shape
+    assert torch.equal(dqkv5[:, :, 1], dk) and torch.equal(dqkv5[:, :, 2], dv)
+    assert (dqkv5[:, :, 0].float() - dq.float()).abs().max() < 1e-2  # dQ accumulates with atomics
+
+    qkv4 = randn(batch, seqlen, heads_q + 2 * heads_kv, d, requires_grad=True)
+    out4 = zigfa.flash_attn_qkvpacked_func(qkv4, causal=True, num_heads_q=heads_q)
+    (dqkv4,) = torch.autograd.grad(out4, qkv4, dout)
+    q, k, v = (x.detach().clone().requires_grad_() for x in qkv4.split([heads_q, heads_kv, heads_kv], dim=2))
+    out = zigfa.flash_attn_func(q, k, v, causal=True)
+    dq, dk, dv = torch.autograd.grad(out, (q, k, v), dout)
+    assert torch.equal(out4, out) and dqkv4.shape == qkv4.shape
+    assert torch.equal(dqkv4[:, :, heads_q : heads_q + heads_kv], dk) and torch.equal(dqkv4[:, :, heads_q + heads_kv :], dv)
+
+    kv = randn(batch, seqlen, 2, heads_kv, d, requires_grad=True)
+    q = randn(batch, seqlen, heads_q, d, requires_grad=True)
+    packed = zigfa.flash_attn_kvpacked_func(q, kv, causal=True)
+    dq_packed, dkv = torch.autograd.grad(packed, (q, kv), dout)
+    k, v = (x.detach().clone().requires_grad_() for x in kv.unbind(2))
+    out = zigfa.flash_attn_func(q, k, v, causal=True)
+    dq, dk, dv = torch.autograd.grad(out, (q, k, v), dout)
+    assert torch.equal(packed, out) and torch.equal(dkv, torch.stack([dk, dv], dim=2))
+
+    lengths = [100, 220]
+    cu = cu_seqlens(lengths)
+    qv, kvv = randn(sum(lengths), heads_q, d, requires_grad=True), randn(sum(lengths), 2, heads_kv, d, requires_grad=True)
+    packed = zigfa.flash_attn_varlen_kvpacked_func(qv, kvv, cu, cu, 220, 220, causal=True)
+    k, v = kvv.unbind(1)
+    assert torch.equal(packed, zigfa.flash_attn_varlen_func(qv, k, v, cu, cu, 220, 220, causal=True))
+    dq_packed, dkv = torch.autograd.grad(packed, (qv, kvv), randn(*packed.shape))
+    assert dkv.shape == kvv.shape and not torch.isnan(dkv).any()
+
+
+def test_irregular_strides_and_misaligned_pointers():
+    torch.manual_seed(5)
+    batch, seqlen, heads, d = 2, 200, 4, 128
+    base = randn(batch, heads, seqlen, d)  # heads-major layout: passed through without a copy
+    q = base.transpose(1, 2)
+    k, v = randn(batch, seqlen, heads, d), randn(batch, seqlen, heads, d)
+    expected = zigfa.flash_attn_func(q.contiguous(), k, v, causal=True)
+    assert torch.equal(zigfa.flash_attn_func(q, k, v, causal=True), expected)
+    # misaligned base pointer and odd strides: copied to a contiguous buffer first
+    storage = randn(batch * seqlen * heads * d + 1)
+    shifted = storage[1:].view(batch, seqlen, heads, d)
+    shifted.copy_(q)
+    assert shifted.data_ptr() % 16 != 0
+    assert torch.equal(zigfa.flash_attn_func(shifted, k, v, causal=True), expected)
+    wide = randn(batch, seqlen, heads, d + 4)[..., :d]
+    wide.copy_(q)
+    assert torch.equal(zigfa.flash_attn_func(wide, k, v, causal=True), expected)
+    # gradients land in strided views
+    leaf = shifted.clone().requires_grad_()
+    out = zigfa.flash_attn_func(leaf.transpose(1, 2).contiguous().transpose(1, 2), k, v, causal=True)
+    (dq,) = torch.autograd.grad(out, leaf, torch.randn_like(out))
+    assert dq.shape == leaf.shape and not torch.isnan(dq).any()
+
+
+def test_invalid_inputs_and_unsupported_options_raise():
+    q, k, v = randn(1, 64, 4, 128), randn(1, 64, 2, 128), randn(1, 64, 2, 128)
+    with pytest.raises(ValueError, match="bfloat16"):
+        zigfa.flash_attn_func(q.half(), k.half(), v.half())
+    with pytest.raises(ValueError, match="head_dim"):
+        zigfa.flash_attn_func(q[..., :80], k[..., :80], v[..., :80])
+    with pytest.raises(ValueError, match="multiple|num_heads_q"):
+        zigfa.flash_attn_func(q[:, :, :3], k, v)
+    with pytest.raises(ValueError, match="window"):
+        zigfa.flash_attn_func(q, k, v, window_size=(-2, 0))
+    with pytest.raises(TypeError, match="window"):
+        zigfa.flash_attn_func(q, k, v, window_size=(1.5, 0))
+    with pytest.raises(ValueError, match="cu_seqlens"):
+        zigfa.flash_attn_varlen_func(q[0], k[0], v[0], torch.zeros(2, device="cuda"), torch.zeros(2, device="cuda"), 64, 64)
+    unsupported = dict(qv=q, q_descale=q, k_descale=q, v_descale=q, attention_chunk=2, softcap=1.0, num_splits=3,
+                       deterministic=True)
+    for name, value in unsupported.items():
+        with pytest.raises(NotImplementedError, match=name):
+            zigfa.flash_attn_func(q, k, v, **{name: value})
+    for name, value in dict(dropout_p=0.1, alibi_slopes=q, softcap=1.0).items():
+        with pytest.raises(NotImplementedError, match=name):
+            zigfa.flash_attn_kvpacked_func(q, torch.stack([k, v], dim=2), **{name: value})
+
+
+def test_no_host_synchronisation_and_graph_replay():
+    q, k, v = randn(2, 512, 8, 128, requires_grad=True), randn(2, 512, 2, 128, requires_grad=True), randn(2, 512, 2, 128, requires_grad=True)
+    dout = randn(2, 512, 8, 128)
+    zigfa.flash_attn_func(q, k, v, causal=True)  # warm up (kernel attributes, allocator)
+    torch.cuda.synchronize()
+    torch.cuda.set_sync_debug_mode("error")
+    try:
+        out = zigfa.flash_attn_func(q, k, v, causal=True)
+        torch.autograd.grad(out, (q, k, v), dout)
+    finally:
+        torch.cuda.set_sync_debug_mode("default")
+    qd, kd, vd = q.detach(), k.detach(), v.detach()
+    expected = zigfa.flash_attn_func(qd, kd, vd, causal=True)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        zigfa.flash_attn_func(qd, kd, vd, causal=True)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            captured = zigfa.flash_attn_func(qd, kd, vd, causal=True)
+    torch.cuda.synchronize()
+    captured.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(captured, expected)

@@ -106,6 +106,7 @@ int* device_status_word() {
 int launch_fwd(const b200fa_fwd_args& args, cudaStream_t stream);
 int launch_bwd(const b200fa_bwd_args& args, cudaStream_t stream);
 size_t bwd_workspace_bytes(const b200fa_problem& problem);
+void arm_bwd_timing(void* const* events);
 
 static int validate_problem(const b200fa_problem& p) {
   B200FA_REQUIRE(p.batch >= 0 && p.seqlen_q >= 0 && p.seqlen_k >= 0, "negative sizes");
@@ -166,6 +167,11 @@ int b200fa_fwd(const b200fa_fwd_args* args, void* stream) {
   B200FA_REQUIRE(args->q && args->out && args->softmax_lse, "null tensor pointer");
   B200FA_REQUIRE(p.seqlen_k == 0 || (args->k && args->v), "null tensor pointer");
   return launch_fwd(*args, static_cast<cudaStream_t>(stream));
+}
+
+int b200fa_bwd_timing_events(void* const* events) {
+  arm_bwd_timing(events);
+  return B200FA_OK;
 }
 
 size_t b200fa_bwd_workspace_bytes(const b200fa_problem* p) { return bwd_workspace_bytes(*p); }

@@ -571,6 +571,17 @@ __global__ void __launch_bounds__(256) bwd_postprocess_kernel(const float* __res
 }
 
 // ---------------------------------------------------------------------------------------------- host side
+static thread_local cudaEvent_t g_timing_events[4];
+static thread_local bool g_timing_armed = false;
+
+void arm_bwd_timing(void* const* events) {
+  g_timing_armed = events != nullptr;
+  for (int i = 0; i < 4 && events; ++i) g_timing_events[i] = static_cast<cudaEvent_t>(events[i]);
+}
+static void mark(int index, cudaStream_t stream) {
+  if (g_timing_armed) cudaEventRecord(g_timing_events[index], stream);
+}
+
 struct BwdWorkspace {
   size_t lse_log2, dpsum, dq_accum, work_list, total;
   int64_t rows, entries;
@@ -661,6 +672,7 @@ static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
   const int64_t tensor_batch = packed ? 1 : bp.batch;
 
   RowMap map{bp.cu_seqlens_q, bp.batch, bp.seqlen_q, w.rows};
+  mark(0, stream);
   if (w.rows > 0) {
     dim3 grid((unsigned)((w.rows + 7) / 8), (unsigned)bp.heads_q);
     bwd_preprocess_kernel<D><<<grid, 256, 0, stream>>>(
@@ -704,10 +716,12 @@ static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
   } else if (run_main) {
     grid = dim3((unsigned)ceil_div(bp.seqlen_k, kBlockN), (unsigned)bp.heads_kv, (unsigned)bp.batch);
   }
+  mark(1, stream);
   if (run_main) {
     int status = launch_main<D>(a, p, grid, dq_accum, w.rows, stream);
     if (status != B200FA_OK) return status;
   }
+  mark(2, stream);
 
   if (w.rows > 0) {
     dim3 post((unsigned)((w.rows + 7) / 8), (unsigned)bp.heads_q);
@@ -715,6 +729,8 @@ static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
                                                         packed ? 0 : a.dq_stride[0], a.dq_stride[1], a.dq_stride[2]);
     B200FA_CUDA_CHECK(cudaGetLastError());
   }
+  mark(3, stream);
+  g_timing_armed = false;
   return B200FA_OK;
 }
 
