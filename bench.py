@@ -1,0 +1,318 @@
+"""Benchmark of the attention hot path on N GPUs of one node.
+
+    python bench.py --gpus N --steps K --warmup W [--workload c1|c4] [--impl reference]
+
+One step = one forward + one backward pass of the workload on every rank. Default workload "c1" is the configuration
+the headline metric is quoted on: fixed-length causal GQA, batch 4, seqlen 8192, 32 query / 8 key heads, head_dim
+128, BF16 N(0,1) inputs from a seed. With N > 1 every rank runs its own copy of that batch (independent shards, no
+collective on the data path; scaling "weak"). Workload "c4" is the long-context sharded configuration (batch 16,
+seqlen 32768, 32/4 heads, window (4096, 0)) split evenly by batch over the ranks (scaling "strong").
+
+The JSON line reports whole-job attention TFLOP/s (forward + backward FLOPs of all ranks / max-over-ranks device
+time; FLOPs = 4 * heads_q * head_dim * visible pairs forward, 2.5x that backward), forward and backward TFLOP/s and
+their fraction of the measured BF16 peak, tokens/s, the end-to-end figure with host buffers, the roofline of the
+dominant kernel (the backward main kernel, timed by itself through the library's timing hook) and a CPU baseline.
+
+`--impl reference` times the CPU restatement of the reference's oracle (oracle/attention_oracle.py; the reference's
+own kernels are Zig -> PTX and cannot be built here) on a bounded sample of the same workload.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT / "zig-flash-attn_b200"))
+
+WORKLOADS = {
+    "c1": dict(batch=4, seqlen=8192, heads_q=32, heads_kv=8, head_dim=128, window=(-1, 0), seed=1,
+               name="fixed-length causal GQA fwd+bwd: batch 4, seqlen 8192, heads 32/8, head_dim 128"),
+    "c4": dict(batch=16, seqlen=32768, heads_q=32, heads_kv=4, head_dim=128, window=(4096, 0), seed=4,
+               name="long-context sharded fwd+bwd: batch 16, seqlen 32768, heads 32/4, head_dim 128, window (4096, 0)"),
+}
+
+
+def visible_pairs(seqlen, window):
+    left, right = window
+    total = 0
+    # closed form per row would do; seqlen <= 32768 so a loop over rows in numpy is cheap
+    import numpy as np
+
+    rows = np.arange(seqlen, dtype=np.int64)
+    hi = np.full(seqlen, seqlen, dtype=np.int64) if right < 0 else np.minimum(seqlen, rows + right + 1)
+    lo = np.zeros(seqlen, dtype=np.int64) if left < 0 else np.maximum(0, rows - left)
+    total = int(np.maximum(hi - lo, 0).sum())
+    return total
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return dict(source="measured", burst=data["bf16_tflops"], sustained=data["bf16_tflops_sustained"],
+                    hbm=data["hbm_gbs"])
+    return dict(source="fallback", burst=1590.0, sustained=1400.0, hbm=6650.0)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.samples, self.process = index, [], None
+
+    def start(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.process = None
+
+    def _read(self):
+        for line in self.process.stdout:
+            self.samples.append([field.strip() for field in line.split(",")])
+
+    def stop(self):
+        if self.process is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.process.terminate()
+        rows = [s for s in self.samples if len(s) == 6 and s[0].isdigit()]
+        if not rows:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["no samples"])
+        clocks = sorted(int(r[0]) for r in rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [name for i, name in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
+        return dict(sm_mhz=clocks[len(clocks) // 2], sm_max_mhz=int(rows[0][1]), reasons=reasons, samples=len(rows))
+
+
+# ------------------------------------------------------------------------------------------------ CPU arm
+def cpu_sample(workload, steps, warmup):
+    """Times the oracle (CPU restatement of the reference's attention oracle) on a bounded sample of the workload:
+    one batch entry and one key head with its query heads, at most the first 8192 rows of the sequence. Returns TFLOP/s."""
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import torch
+
+    import attention_oracle as oracle
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    group = workload["heads_q"] // workload["heads_kv"]
+    seqlen = min(workload["seqlen"], 8192)
+    d = workload["head_dim"]
+    torch.manual_seed(workload["seed"])
+    q = torch.randn(1, seqlen, group, d, dtype=torch.bfloat16)
+    k, v = (torch.randn(1, seqlen, 1, d, dtype=torch.bfloat16) for _ in range(2))
+    dout = torch.randn(1, seqlen, group, d, dtype=torch.bfloat16)
+    flops = 3.5 * 4 * group * d * visible_pairs(seqlen, workload["window"])
+    times = []
+    for step in range(warmup + steps):
+        start = time.perf_counter()
+        oracle.gradients(oracle.attention, q, k, v, dout, window_size=workload["window"])
+        if step >= warmup:
+            times.append(time.perf_counter() - start)
+    seconds = sum(times) / len(times)
+    sample = f"batch 1, {group} query heads / 1 key head, first {seqlen} rows of the sequence, fp32 math, fwd+bwd"
+    return dict(value=flops / seconds / 1e12, unit="TFLOP/s", cores=threads, kind="port", sample=sample,
+                seconds_per_step=seconds)
+
+
+def reference_arm(options, workload):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warmup = min(options.steps, 5), min(options.warmup, 1)
+    result = cpu_sample(workload, steps, warmup)
+    line = {
+        "impl": "reference", "metric": "attn_fwd_bwd_tflops", "value": result["value"], "unit": "TFLOP/s",
+        "n_gpus": options.gpus, "steps": steps, "warmup": warmup, "ms_per_step": result["seconds_per_step"] * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload["name"]},
+        "cpu_baseline": {k: result[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": result["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "reference's own kernels are Zig->PTX (zig-nvptx fork + cuda-core absent): CPU port of its oracle timed instead",
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------ GPU arm
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=10)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--workload", choices=sorted(WORKLOADS), default="c1")
+    parser.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    parser.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg")
+    options = parser.parse_args()
+    workload = WORKLOADS[options.workload]
+    if options.impl == "reference":
+        return reference_arm(options, workload)
+
+    import torch
+    import torch.distributed as dist
+
+    import zigfa
+    from zigfa._impl import lib, ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    warmup = max(options.warmup, 3)
+    steps = options.steps
+
+    strong = options.workload == "c4"
+    batch = workload["batch"] // world if strong else workload["batch"]
+    seqlen, heads_q, heads_kv, d = workload["seqlen"], workload["heads_q"], workload["heads_kv"], workload["head_dim"]
+    window = workload["window"]
+    causal = window == (-1, 0)
+    generator = torch.Generator(device="cpu").manual_seed(workload["seed"] * 1000 + rank)
+    shapes = dict(q=(batch, seqlen, heads_q, d), k=(batch, seqlen, heads_kv, d), v=(batch, seqlen, heads_kv, d),
+                  dout=(batch, seqlen, heads_q, d))
+    # host buffers are pinned; the resident copies are made once, before the timed region
+    host = {}
+    for name, shape in shapes.items():
+        buffer = torch.empty(shape, dtype=torch.bfloat16).pin_memory()
+        for b in range(batch):  # fill per batch entry to bound the float32 temporary
+            buffer[b] = torch.randn(shape[1:], generator=generator, dtype=torch.float32).to(torch.bfloat16)
+        host[name] = buffer
+    resident = {name: tensor.to(device) for name, tensor in host.items()}
+    pairs = batch * visible_pairs(seqlen, window)
+    flops_fwd = 4.0 * heads_q * d * pairs
+    flops_bwd = 2.5 * flops_fwd
+    tokens = batch * seqlen
+    scale = d**-0.5
+    left, right = window
+
+    q, k, v, dout = (resident[name] for name in ("q", "k", "v", "dout"))
+    out = torch.empty_like(q)
+    lse = torch.empty(batch, heads_q, seqlen, dtype=torch.float32, device=device)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+    def forward():
+        ops.launch_forward(q, k, v, out, lse, None, None, scale, left, right)
+
+    def backward():
+        ops.launch_backward(dout, q, k, v, out, lse, dq, dk, dv, None, None, scale, left, right)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(function, count):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        start.record()
+        for _ in range(count):
+            function()
+        stop.record()
+        barrier()
+        elapsed = torch.tensor([start.elapsed_time(stop) / count], device=device)
+        if world > 1:
+            dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+        return elapsed.item()
+
+    def step():
+        forward()
+        backward()
+
+    for _ in range(warmup):
+        step()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms_step = timed(step, steps)
+    ms_fwd = timed(forward, steps)
+    ms_bwd = timed(backward, steps)
+
+    # dominant kernel by itself: the backward main kernel between the library's timing events
+    events = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    for event in events:
+        event.record()
+    torch.cuda.synchronize()
+    handles = (ctypes.c_void_p * 4)(*[event.cuda_event for event in events])
+    main_ms, pre_ms, post_ms = [], [], []
+    for _ in range(max(3, min(steps, 10))):
+        lib.library().b200fa_bwd_timing_events(handles)
+        backward()
+        torch.cuda.synchronize()
+        pre_ms.append(events[0].elapsed_time(events[1]))
+        main_ms.append(events[1].elapsed_time(events[2]))
+        post_ms.append(events[2].elapsed_time(events[3]))
+    ms_main = sum(main_ms) / len(main_ms)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # end to end through the public API with host buffers
+    def e2e_step():
+        dq_, dk_, dv_ = None, None, None
+        qd = host["q"].to(device, non_blocking=True).requires_grad_()
+        kd = host["k"].to(device, non_blocking=True).requires_grad_()
+        vd = host["v"].to(device, non_blocking=True).requires_grad_()
+        dd = host["dout"].to(device, non_blocking=True)
+        result = zigfa.flash_attn_func(qd, kd, vd, causal=causal, window_size=(left, -1 if causal else right))
+        dq_, dk_, dv_ = torch.autograd.grad(result, (qd, kd, vd), dd)
+        for name, tensor in (("out", result.detach()), ("dq", dq_), ("dk", dk_), ("dv", dv_)):
+            host_out[name].copy_(tensor, non_blocking=True)
+
+    host_out = {name: torch.empty(shapes[key], dtype=torch.bfloat16).pin_memory()
+                for name, key in (("out", "q"), ("dq", "q"), ("dk", "k"), ("dv", "v"))}
+    e2e_step()
+    ms_e2e = timed(e2e_step, max(2, min(steps, 5)))
+    h2d = sum(t.numel() * 2 for t in host.values())
+    d2h = sum(t.numel() * 2 for t in host_out.values())
+    status = lib.library().b200fa_device_status()
+
+    if rank == 0:
+        peaks = measured_peaks()
+        total_flops = (flops_fwd + flops_bwd) * world
+        value = total_flops / (ms_step * 1e-3) / 1e12
+        line = {
+            "metric": "attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": workload["name"], "per_gpu_batch": batch, "global_batch": batch * world,
+                       "seq_len": seqlen, "parallelism": f"batch shards x{world}, no collective on the data path",
+                       "l2": "inputs (675 MB+) exceed the 126 MB L2", "flop_convention": "4*Hq*D*visible_pairs fwd, 2.5x bwd"},
+            "fwd_tflops_per_gpu": flops_fwd / (ms_fwd * 1e-3) / 1e12,
+            "bwd_tflops_per_gpu": flops_bwd / (ms_bwd * 1e-3) / 1e12,
+            "fwd_frac_of_peak": flops_fwd / (ms_fwd * 1e-3) / 1e12 / peaks["burst"],
+            "bwd_frac_of_peak": flops_bwd / (ms_bwd * 1e-3) / 1e12 / peaks["burst"],
+            "fwd_frac_of_nominal_2250": flops_fwd / (ms_fwd * 1e-3) / 1e12 / 2250.0,
+            "bwd_frac_of_nominal_2250": flops_bwd / (ms_bwd * 1e-3) / 1e12 / 2250.0,
+            "tokens_per_s": tokens * world / (ms_step * 1e-3),
+            "ms_fwd": ms_fwd, "ms_bwd": ms_bwd,
+            "bwd_kernel_ms": {"preprocess": sum(pre_ms) / len(pre_ms), "main": ms_main, "postprocess": sum(post_ms) / len(post_ms)},
+            "gpu_launches": steps * 4,
+            "e2e": {"value": total_flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "roofline": {"kernel": "bwd_kernel<128> (dK/dV/dQ main)", "bound": "tensor",
+                         "achieved": flops_bwd / (ms_main * 1e-3) / 1e12, "peak": peaks["burst"], "unit": "TFLOP/s",
+                         "frac": flops_bwd / (ms_main * 1e-3) / 1e12 / peaks["burst"], "traffic": None,
+                         "peak_source": f"{peaks['source']} cuBLAS BF16 burst", "sustained_peak": peaks["sustained"]},
+            "roofline_fwd": {"kernel": "fwd_kernel<128>", "bound": "tensor", "achieved": flops_fwd / (ms_fwd * 1e-3) / 1e12,
+                             "peak": peaks["burst"], "unit": "TFLOP/s",
+                             "frac": flops_fwd / (ms_fwd * 1e-3) / 1e12 / peaks["burst"]},
+            "clocks": clocks, "device_status": status,
+        }
+        if not options.skip_cpu and world >= 1:
+            line["cpu_baseline"] = {k: v for k, v in cpu_sample(workload, 3, 1).items() if k != "seconds_per_step"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

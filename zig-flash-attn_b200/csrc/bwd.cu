@@ -313,72 +313,76 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         }
         if (!key_valid) qhi = 0;
         const bool masked = __any_sync(0xffffffffu, qlo > cb || qhi < cb + 64);
-        // ---- P^T
+        // ---- P^T (kept in FP32 registers for dS, stored to TMEM as BF16 for the dV MMA)
         if (!mbar_wait_warp(bar_s_full, it & 1, wctx, kWaitBwdCompute)) { ok = false; break; }
         tc_fence_after();
-        uint32_t pk[32];
-        {
-          float sc[64];
-          tmem_ld32(t_s + cb, reinterpret_cast<uint32_t*>(sc));
-          tmem_ld32(t_s + cb + 32, reinterpret_cast<uint32_t*>(sc) + 32);
-          tc_wait_ld();
+        float pf[64];
+        tmem_ld32(t_s + cb, reinterpret_cast<uint32_t*>(pf));
+        tmem_ld32(t_s + cb + 32, reinterpret_cast<uint32_t*>(pf) + 32);
+        tc_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float4 l4 = ld_shared_f4(smem_lse + st * 512 + (cb + 4 * j) * 4);
-            float p0 = ex2_approx(fmaf(sc[4 * j + 0], p.scale_log2, -l4.x));
-            float p1 = ex2_approx(fmaf(sc[4 * j + 1], p.scale_log2, -l4.y));
-            float p2 = ex2_approx(fmaf(sc[4 * j + 2], p.scale_log2, -l4.z));
-            float p3 = ex2_approx(fmaf(sc[4 * j + 3], p.scale_log2, -l4.w));
-            if (masked) {
-              const int q = cb + 4 * j;
-              p0 = (q + 0 >= qlo && q + 0 < qhi) ? p0 : 0.f;
-              p1 = (q + 1 >= qlo && q + 1 < qhi) ? p1 : 0.f;
-              p2 = (q + 2 >= qlo && q + 2 < qhi) ? p2 : 0.f;
-              p3 = (q + 3 >= qlo && q + 3 < qhi) ? p3 : 0.f;
-            }
-            pk[2 * j] = pack_bf16x2(p0, p1);
-            pk[2 * j + 1] = pack_bf16x2(p2, p3);
+        for (int j = 0; j < 16; ++j) {
+          const float4 l4 = ld_shared_f4(smem_lse + st * 512 + (cb + 4 * j) * 4);
+          float p0 = ex2_approx(fmaf(pf[4 * j + 0], p.scale_log2, -l4.x));
+          float p1 = ex2_approx(fmaf(pf[4 * j + 1], p.scale_log2, -l4.y));
+          float p2 = ex2_approx(fmaf(pf[4 * j + 2], p.scale_log2, -l4.z));
+          float p3 = ex2_approx(fmaf(pf[4 * j + 3], p.scale_log2, -l4.w));
+          if (masked) {
+            const int q = cb + 4 * j;
+            p0 = (q + 0 >= qlo && q + 0 < qhi) ? p0 : 0.f;
+            p1 = (q + 1 >= qlo && q + 1 < qhi) ? p1 : 0.f;
+            p2 = (q + 2 >= qlo && q + 2 < qhi) ? p2 : 0.f;
+            p3 = (q + 3 >= qlo && q + 3 < qhi) ? p3 : 0.f;
           }
+          pf[4 * j + 0] = p0;
+          pf[4 * j + 1] = p1;
+          pf[4 * j + 2] = p2;
+          pf[4 * j + 3] = p3;
         }
         // P^T of a group goes over the first 32 columns of the group's own S^T columns.
-        tmem_st16(t_s + cb, pk);
-        tmem_st16(t_s + cb + 16, pk + 16);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(pf[32 * h + 2 * i], pf[32 * h + 2 * i + 1]);
+          tmem_st16(t_s + cb + 16 * h, pk);
+        }
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar_p_full);
-        // ---- dS^T
+        // ---- dS^T = P^T o (dP^T - D), written to shared memory as BF16
         if (!mbar_wait_warp(bar_dp_full, it & 1, wctx, kWaitBwdCompute)) { ok = false; break; }
+        // The dS tile of the previous iteration must have been consumed by its dK and dQ MMAs.
+        if (it > 0 && !mbar_wait_warp(bar_dq_full, (it - 1) & 1, wctx, kWaitBwdCompute)) { ok = false; break; }
         tc_fence_after();
-        uint32_t dsk[32];
-        {
-          float dp[64];
-          tmem_ld32(t_dp + cb, reinterpret_cast<uint32_t*>(dp));
-          tmem_ld32(t_dp + cb + 32, reinterpret_cast<uint32_t*>(dp) + 32);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float dp[32];
+          tmem_ld32(t_dp + cb + 32 * h, reinterpret_cast<uint32_t*>(dp));
           tc_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float4 d4 = ld_shared_f4(smem_dpsum + (cb + 4 * j) * 4);
-            const float p0 = __uint_as_float(pk[2 * j] << 16), p1 = __uint_as_float(pk[2 * j] & 0xffff0000u);
-            const float p2 = __uint_as_float(pk[2 * j + 1] << 16), p3 = __uint_as_float(pk[2 * j + 1] & 0xffff0000u);
-            float s0 = p0 * (dp[4 * j + 0] - d4.x), s1 = p1 * (dp[4 * j + 1] - d4.y);
-            float s2 = p2 * (dp[4 * j + 2] - d4.z), s3 = p3 * (dp[4 * j + 3] - d4.w);
-            if (masked) {
-              const int q = cb + 4 * j;
-              s0 = (q + 0 >= qlo && q + 0 < qhi) ? s0 : 0.f;
-              s1 = (q + 1 >= qlo && q + 1 < qhi) ? s1 : 0.f;
-              s2 = (q + 2 >= qlo && q + 2 < qhi) ? s2 : 0.f;
-              s3 = (q + 3 >= qlo && q + 3 < qhi) ? s3 : 0.f;
+          for (int j = 0; j < 4; ++j) {  // 8 queries = one 16-byte chunk
+            uint32_t packed[4];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int i = 8 * j + 4 * e;  // column within this half
+              const float4 d4 = ld_shared_f4(smem_dpsum + (cb + 32 * h + i) * 4);
+              float s0 = pf[32 * h + i + 0] * (dp[i + 0] - d4.x), s1 = pf[32 * h + i + 1] * (dp[i + 1] - d4.y);
+              float s2 = pf[32 * h + i + 2] * (dp[i + 2] - d4.z), s3 = pf[32 * h + i + 3] * (dp[i + 3] - d4.w);
+              if (masked) {
+                const int q = cb + 32 * h + i;
+                s0 = (q + 0 >= qlo && q + 0 < qhi) ? s0 : 0.f;
+                s1 = (q + 1 >= qlo && q + 1 < qhi) ? s1 : 0.f;
+                s2 = (q + 2 >= qlo && q + 2 < qhi) ? s2 : 0.f;
+                s3 = (q + 3 >= qlo && q + 3 < qhi) ? s3 : 0.f;
+              }
+              packed[2 * e] = pack_bf16x2(s0, s1);
+              packed[2 * e + 1] = pack_bf16x2(s2, s3);
             }
-            dsk[2 * j] = pack_bf16x2(s0, s1);
-            dsk[2 * j + 1] = pack_bf16x2(s2, s3);
+            st_shared_v4(ds_row + (((4 * h + j) ^ (r & 7)) << 4), packed[0], packed[1], packed[2], packed[3]);
           }
         }
         tc_fence_before();
-        // The dS tile of the previous iteration must have been consumed by its dK and dQ MMAs.
-        if (it > 0 && !mbar_wait_warp(bar_dq_full, (it - 1) & 1, wctx, kWaitBwdCompute)) { ok = false; break; }
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          st_shared_v4(ds_row + ((j ^ (r & 7)) << 4), dsk[4 * j], dsk[4 * j + 1], dsk[4 * j + 2], dsk[4 * j + 3]);
         fence_proxy_async_smem();
         mbar_arrive(bar_ds_full);
         ++it;
