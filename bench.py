@@ -20,7 +20,6 @@ import argparse
 import ctypes
 import json
 import os
-import subprocess
 import sys
 import threading
 import time
@@ -60,38 +59,51 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons through NVML (read-only) while the timed region runs."""
 
-    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, index):
-        self.index, self.samples, self.process = index, [], None
+        self.index, self.samples, self.running, self.thread, self.error = index, [], False, None, None
 
     def start(self):
         try:
-            self.process = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            threading.Thread(target=self._read, daemon=True).start()
-        except OSError:
-            self.process = None
+            import pynvml
 
-    def _read(self):
-        for line in self.process.stdout:
-            self.samples.append([field.strip() for field in line.split(",")])
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception as error:  # NVML missing: report that instead of clocks
+            self.error = f"nvml unavailable: {error}"
+            return
+        self.running = True
+        self.thread = threading.Thread(target=self._poll, daemon=True)
+        self.thread.start()
+
+    def _poll(self):
+        while self.running:
+            try:
+                clock = self.nvml.nvmlDeviceGetClockInfo(self.handle, self.nvml.NVML_CLOCK_SM)
+                reasons = self.nvml.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                self.samples.append((clock, reasons))
+            except Exception as error:
+                self.error = str(error)
+                return
+            time.sleep(0.05)
 
     def stop(self):
-        if self.process is None:
-            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
-        self.process.terminate()
-        rows = [s for s in self.samples if len(s) == 6 and s[0].isdigit()]
-        if not rows:
-            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["no samples"])
-        clocks = sorted(int(r[0]) for r in rows)
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [name for i, name in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
-        return dict(sm_mhz=clocks[len(clocks) // 2], sm_max_mhz=int(rows[0][1]), reasons=reasons, samples=len(rows))
+        self.running = False
+        if self.thread is not None:
+            self.thread.join(timeout=1)
+        if not self.samples:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=[self.error or "no samples"])
+        clocks = sorted(clock for clock, _ in self.samples)
+        seen = 0
+        for _, reasons in self.samples:
+            seen |= reasons
+        reasons = [name for bit, name in self.REASONS.items() if seen & bit]
+        return dict(sm_mhz=clocks[len(clocks) // 2], sm_max_mhz=self.max_mhz, reasons=reasons, samples=len(clocks))
 
 
 # ------------------------------------------------------------------------------------------------ CPU arm

@@ -50,9 +50,9 @@ struct BwdConfig {
   static constexpr int kOffDo = kOffQ + 2 * kTileBytes;
   static constexpr int kOffDs = kOffDo + kTileBytes;
   static constexpr int kOffStage = kOffDs + kDsBytes;    // two staging buffers
-  static constexpr int kOffStats = kOffStage + 2 * kStageBytes;  // lse[2][128], dpsum[128] floats
-  static constexpr int kOffBars = kOffStats + 3 * 512;
-  static constexpr int kSmemBytes = kOffBars + 256 + 1024;
+  static constexpr int kOffStats = kOffStage + 2 * kStageBytes;  // lse[2][128], dpsum[2][128] floats
+  static constexpr int kOffBars = kOffStats + 4 * 512;
+  static constexpr int kSmemBytes = kOffBars + 128;
   static constexpr int kThreads = 448;
   static constexpr int kTmemS = 0, kTmemDp = 128, kTmemDv = 256, kTmemDk = 256 + D;
 };
@@ -101,8 +101,12 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   const int group = pr.heads_q / pr.heads_kv;
   const int64_t stat_base = pr.cu_q ? 0 : (int64_t)seq * pr.seqlen_q;
 
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  if (base & 1023u) {  // the swizzled tiles need 1024-byte alignment; report instead of computing garbage
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, (kWaitBwdLoad << 16) | 0xffff);
+    return;
+  }
   const uint32_t smem_k = base + Cfg::kOffK, smem_v = base + Cfg::kOffV, smem_q = base + Cfg::kOffQ;
   const uint32_t smem_do = base + Cfg::kOffDo, smem_ds = base + Cfg::kOffDs, smem_stage = base + Cfg::kOffStage;
   const uint32_t smem_lse = base + Cfg::kOffStats, smem_dpsum = smem_lse + 1024;
@@ -206,7 +210,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const int r = lane + 32 * k;
-          if (row0 + r < p.rows) cp_async_4(smem_dpsum + r * 4, dpsum_head + row0 + r);
+          if (row0 + r < p.rows) cp_async_4(smem_dpsum + st * 512 + r * 4, dpsum_head + row0 + r);
         }
         cp_async_arrive_noinc(bar_do_full);
         ++it;
@@ -366,7 +370,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
               const int i = 8 * j + 4 * e;  // column within this half
-              const float4 d4 = ld_shared_f4(smem_dpsum + (cb + 32 * h + i) * 4);
+              const float4 d4 = ld_shared_f4(smem_dpsum + st * 512 + (cb + 32 * h + i) * 4);
               float s0 = pf[32 * h + i + 0] * (dp[i + 0] - d4.x), s1 = pf[32 * h + i + 1] * (dp[i + 1] - d4.y);
               float s2 = pf[32 * h + i + 2] * (dp[i + 2] - d4.z), s3 = pf[32 * h + i + 3] * (dp[i + 3] - d4.w);
               if (masked) {

@@ -521,6 +521,7 @@ def _run_forward(ctx, q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seq
                  return_softmax):
     softmax_scale = default_softmax_scale(softmax_scale, q.shape[-1])
     left, right = window_size
+    require_window(left, right)
     window = (left, 0 if causal else right)
     if cu_seqlens_q is None:
         max_seqlen_q, max_seqlen_k = q.shape[1], k.shape[1]
@@ -647,6 +648,7 @@ def _run_inter_sequence_forward(ctx, q, k, v, cu_seqlens_q, cu_seqlens_k, visibi
     reject_unsupported(deterministic=deterministic)
     softmax_scale = default_softmax_scale(softmax_scale, q.shape[-1])
     window = _inter_sequence_window(causal, window_size, window_sizes)
+    require_window(*window_size)
     if metadata is None:
         metadata = prepare_inter_sequence_metadata(cu_seqlens_q, cu_seqlens_k, visibility_bits)
     layout = (cu_seqlens_q, cu_seqlens_k, visibility_bits, *metadata._tensors, window_sizes)
