@@ -31,6 +31,8 @@ sys.path.insert(0, str(ROOT / "zig-flash-attn_b200"))
 WORKLOADS = {
     "c1": dict(batch=4, seqlen=8192, heads_q=32, heads_kv=8, head_dim=128, window=(-1, 0), seed=1,
                name="fixed-length causal GQA fwd+bwd: batch 4, seqlen 8192, heads 32/8, head_dim 128"),
+    "c1s": dict(batch=1, seqlen=8192, heads_q=32, heads_kv=8, head_dim=128, window=(-1, 0), seed=1,
+                name="one batch entry of c1 (profiling case): batch 1, seqlen 8192, heads 32/8, head_dim 128, causal"),
     "c4": dict(batch=16, seqlen=32768, heads_q=32, heads_kv=4, head_dim=128, window=(4096, 0), seed=4,
                name="long-context sharded fwd+bwd: batch 16, seqlen 32768, heads 32/4, head_dim 128, window (4096, 0)"),
 }
@@ -164,6 +166,7 @@ def main():
     parser.add_argument("--workload", choices=sorted(WORKLOADS), default="c1")
     parser.add_argument("--impl", choices=["b200", "reference"], default="b200")
     parser.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg")
+    parser.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     options = parser.parse_args()
     workload = WORKLOADS[options.workload]
     if options.impl == "reference":
@@ -281,8 +284,11 @@ def main():
 
     host_out = {name: torch.empty(shapes[key], dtype=torch.bfloat16).pin_memory()
                 for name, key in (("out", "q"), ("dq", "q"), ("dk", "k"), ("dv", "v"))}
-    e2e_step()
-    ms_e2e = timed(e2e_step, max(2, min(steps, 5)))
+    if options.skip_e2e:
+        ms_e2e = float("nan")
+    else:
+        e2e_step()
+        ms_e2e = timed(e2e_step, max(2, min(steps, 5)))
     h2d = sum(t.numel() * 2 for t in host.values())
     d2h = sum(t.numel() * 2 for t in host_out.values())
     status = lib.library().b200fa_device_status()
