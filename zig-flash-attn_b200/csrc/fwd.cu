@@ -41,7 +41,7 @@ struct FwdConfig {
   static constexpr int kSmemQ = 2 * kTileBytes;
   static constexpr int kSmemKv = kStages * kTileBytes;
   static constexpr int kSmemBytes = kSmemQ + kSmemKv + 1024 /*alignment slack*/ + 256 /*barriers*/;
-  static constexpr int kThreads = 320;
+  static constexpr int kThreads = 384;  // 2 softmax warpgroups + 1 warpgroup holding the MMA and TMA warps
   static constexpr int kTmemS = 0;
   static constexpr int kTmemO = 256;
 };
@@ -82,6 +82,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
            const __grid_constant__ CUtensorMap map_v, const __grid_constant__ FwdParams p) {
   using Cfg = FwdConfig<D>;
   constexpr int NS = Cfg::kStages;
+  // Register split between the warpgroups: 2 x 128 x 200 + 128 x 96 = 63488 of 65536.
+  constexpr int kRegsSoftmax = 200, kRegsOther = 96;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t smem_q = smem_base;
@@ -137,7 +139,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   const uint32_t tmem_base = *tmem_ptr_smem;
   const Problem& pr = p.prob;
 
-  if (warp == 9) {
+  // setmaxnreg is executed once per warpgroup, by all four of its warps at the same instruction.
+  if (warp >= 8) {
+   setmaxnreg_dec<kRegsOther>();
+   if (warp == 9) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t ring = 0;      // K/V slots issued so far
@@ -174,7 +179,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         }
       }
     }
-  } else if (warp == 8) {
+   } else if (warp == 8) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(kBlockM, kBlockN, 0, 0);
@@ -193,7 +198,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       auto issue_pv = [&](int stage, uint32_t v_smem, bool accumulate) {
 #pragma unroll
         for (int kk = 0; kk < kBlockN / 16; ++kk) {
-          umma_ts(tmem_base + Cfg::kTmemO + stage * D, tmem_base + Cfg::kTmemS + stage * 128 + kk * 8,
+          umma_ts(tmem_base + Cfg::kTmemO + stage * D, tmem_base + Cfg::kTmemS + stage * 128 + 64 + kk * 8,
                   umma_smem_desc(v_smem + kk * 2048, Cfg::kPanelBytes, 1024), idesc_pv, accumulate || kk > 0);
         }
       };
@@ -259,8 +264,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       // The last commit of this thread must land before the CTA may exit.
       if (ok && q_count > 0) mbar_wait(bar_q_empty, (q_count - 1) & 1, wctx, kWaitQEmpty);
     }
+   }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue (one thread per row)
+    setmaxnreg_inc<kRegsSoftmax>();
     const int stage = warp >> 2;
     const int row_in_stage = (warp & 3) * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -285,15 +292,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       while (cur.next(&kb)) {
         if (!mbar_wait_warp(my_s_full, blocks & 1, wctx, kWaitSFull)) { ok = false; break; }
         tc_fence_after();
-        float s[128];
-        {
-          uint32_t* r = reinterpret_cast<uint32_t*>(s);
-          tmem_ld32(t_s, r);
-          tmem_ld32(t_s + 32, r + 32);
-          tmem_ld32(t_s + 64, r + 64);
-          tmem_ld32(t_s + 96, r + 96);
-          tc_wait_ld();
-        }
+        // Column limits of this row inside the block; `masked` is uniform over the warp.
         int lo, hi;
         if (kb.banded) {
           lo = band_lo - kb.col0;
@@ -302,19 +301,41 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           lo = 0;
           hi = kb.limit - kb.col0;
         }
-        if (__any_sync(0xffffffffu, lo > 0 || hi < kBlockN)) {
+        const bool masked = __any_sync(0xffffffffu, lo > 0 || hi < kBlockN);
+        auto apply_mask = [&](float2* values, int first_column) {
 #pragma unroll
-          for (int c = 0; c < 128; ++c) s[c] = (c >= lo && c < hi) ? s[c] : -INFINITY;
-        }
-        float bm0 = s[0], bm1 = s[1], bm2 = s[2], bm3 = s[3];
+          for (int i = 0; i < 32; ++i) {
+            const int c = first_column + 2 * i;
+            values[i].x = (c >= lo && c < hi) ? values[i].x : -INFINITY;
+            values[i].y = (c + 1 >= lo && c + 1 < hi) ? values[i].y : -INFINITY;
+          }
+        };
+        auto max_of = [&](const float2* values) {
+          float a = fmaxf(values[0].x, values[0].y), b = fmaxf(values[1].x, values[1].y);
+          float c = fmaxf(values[2].x, values[2].y), d = fmaxf(values[3].x, values[3].y);
 #pragma unroll
-        for (int c = 4; c < 128; c += 4) {
-          bm0 = fmaxf(bm0, s[c]);
-          bm1 = fmaxf(bm1, s[c + 1]);
-          bm2 = fmaxf(bm2, s[c + 2]);
-          bm3 = fmaxf(bm3, s[c + 3]);
-        }
-        const float m_new = fmaxf(m, fmaxf(fmaxf(bm0, bm1), fmaxf(bm2, bm3)));
+          for (int i = 4; i < 32; i += 4) {
+            a = fmaxf(a, fmaxf(values[i].x, values[i].y));
+            b = fmaxf(b, fmaxf(values[i + 1].x, values[i + 1].y));
+            c = fmaxf(c, fmaxf(values[i + 2].x, values[i + 2].y));
+            d = fmaxf(d, fmaxf(values[i + 3].x, values[i + 3].y));
+          }
+          return fmaxf(fmaxf(a, b), fmaxf(c, d));
+        };
+        // Pass 1: row maximum. Columns [0,64) are read for the maximum only and read again in pass 2; columns
+        // [64,128) stay in registers. P (BF16) goes over columns [64,128) of S, upper half first, so nothing that is
+        // still to be read gets overwritten.
+        float2 low[32], high[32];
+        tmem_ld32(t_s, reinterpret_cast<uint32_t*>(low));
+        tmem_ld32(t_s + 32, reinterpret_cast<uint32_t*>(low) + 32);
+        tc_wait_ld();
+        if (masked) apply_mask(low, 0);
+        const float max_low = max_of(low);
+        tmem_ld32(t_s + 64, reinterpret_cast<uint32_t*>(high));
+        tmem_ld32(t_s + 96, reinterpret_cast<uint32_t*>(high) + 32);
+        tc_wait_ld();
+        if (masked) apply_mask(high, 64);
+        const float m_new = fmaxf(m, fmaxf(max_low, max_of(high)));
         const bool grow = (m_new - m) * scale_log2 > 8.f;  // also true when m is -inf and m_new is finite
         if (__any_sync(0xffffffffu, grow)) {
           float alpha = 1.f;
@@ -326,33 +347,46 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           if (tile_blocks > 0) {
             if (!mbar_wait_warp(my_pv_done, (blocks - 1) & 1, wctx, kWaitPvDone)) { ok = false; break; }
             tc_fence_after();
+            const float2 alpha2 = make_float2(alpha, alpha);
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
-              uint32_t o[32];
-              tmem_ld32(t_o + 32 * c, o);
+              float2 o[16];
+              tmem_ld32(t_o + 32 * c, reinterpret_cast<uint32_t*>(o));
               tc_wait_ld();
 #pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-              tmem_st32(t_o + 32 * c, o);
+              for (int i = 0; i < 16; ++i) o[i] = __fmul2_rn(o[i], alpha2);
+              tmem_st32(t_o + 32 * c, reinterpret_cast<uint32_t*>(o));
             }
           }
         }
         const float mc = (m == -INFINITY) ? 0.f : m * scale_log2;
-        float l0 = 0.f, l1 = 0.f;
+        const float2 scale2 = make_float2(scale_log2, scale_log2), shift2 = make_float2(-mc, -mc);
+        float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
+        // 64 scores -> 64 probabilities (BF16) stored at P columns [first_p_column, first_p_column + 32)
+        auto exponentiate = [&](const float2* values, uint32_t first_p_column) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t packed[16];
+          for (int c = 0; c < 2; ++c) {
+            uint32_t packed[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float p0 = ex2_approx(fmaf(s[32 * c + 2 * i], scale_log2, -mc));
-            const float p1 = ex2_approx(fmaf(s[32 * c + 2 * i + 1], scale_log2, -mc));
-            l0 += p0;
-            l1 += p1;
-            packed[i] = pack_bf16x2(p0, p1);
+            for (int i = 0; i < 16; ++i) {
+              const float2 x = __ffma2_rn(values[16 * c + i], scale2, shift2);
+              float2 e;
+              e.x = ex2_approx(x.x);
+              e.y = ex2_approx(x.y);
+              if (i & 1) sum_b = __fadd2_rn(sum_b, e); else sum_a = __fadd2_rn(sum_a, e);
+              packed[i] = pack_bf16x2(e.x, e.y);
+            }
+            tmem_st16(t_s + 64 + first_p_column + 16 * c, packed);
           }
-          tmem_st16(t_s + 16 * c, packed);
-        }
-        l += l0 + l1;
+        };
+        // Pass 2 for columns [0,64): the loads are in flight while the upper half is exponentiated.
+        tmem_ld32(t_s, reinterpret_cast<uint32_t*>(low));
+        tmem_ld32(t_s + 32, reinterpret_cast<uint32_t*>(low) + 32);
+        exponentiate(high, 32);
+        tc_wait_ld();
+        if (masked) apply_mask(low, 0);
+        exponentiate(low, 0);
+        l += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(my_p_full);

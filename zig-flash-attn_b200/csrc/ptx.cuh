@@ -79,7 +79,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Bounded wait on the phase with the given parity.
-static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, WaitCtx ctx, int code) {
+__device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, WaitCtx ctx, int code) {
   const unsigned long long start = global_timer_ns();
   for (;;) {
 #pragma unroll 1
@@ -246,6 +246,16 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
       :
       : "r"(taddr), B200FA_I16(r, 0), B200FA_I16(r, 16)
       : "memory");
+}
+
+// ---------------------------------------------------------------- register reallocation between warpgroups
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
 // ---------------------------------------------------------------- small math helpers
