@@ -26,8 +26,8 @@ constexpr float kLog2e = 1.4426950408889634f;
 struct BwdParams {
   Problem prob;
   float scale, scale_log2;
-  const float* lse_log2;  // (heads_q, rows) : lse * log2(e), +inf for rows without keys
-  const float* dpsum;     // (heads_q, rows) : sum_d O * dO
+  const float* lse_log2;  // (heads_q, rows) : -lse * log2(e)
+  const float* dpsum;     // (heads_q, rows) : -sum_d O * dO
   int64_t rows;           // rows of the statistics / dQ accumulator per head (batch * seqlen_q or total_q)
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;
@@ -53,7 +53,7 @@ struct BwdConfig {
   static constexpr int kOffStats = kOffStage + 2 * kStageBytes;  // lse[2][128], dpsum[2][128] floats
   static constexpr int kOffBars = kOffStats + 4 * 512;
   static constexpr int kSmemBytes = kOffBars + 128;
-  static constexpr int kThreads = 448;
+  static constexpr int kThreads = 512;  // 2 compute warpgroups, 1 dQ-drain warpgroup, 1 warpgroup with the MMA and load warps
   static constexpr int kTmemS = 0, kTmemDp = 128, kTmemDv = 256, kTmemDk = 256 + D;
 };
 
@@ -160,7 +160,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   }
   const int iterations = blocks_per_head * group;
 
-  if (warp == 13) {
+  // Register split (setmaxnreg, one site per warpgroup): 2 x 128 x 168 + 128 x 96 + 128 x 80 = 65536.
+  if (warp >= 12) {
+   setmaxnreg_dec<80>();
+   if (warp == 13) {
     // ------------------------------------------------------------------ loads
     if (lane == 0) {
       tma_prefetch_descriptor(&map_q);
@@ -216,7 +219,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         ++it;
       }
     }
-  } else if (warp == 12) {
+   } else if (warp == 12) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && iterations > 0) {
       constexpr uint32_t idesc_st = umma_idesc_bf16(128, 128, 0, 0);   // S^T, dP^T
@@ -289,7 +292,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       }
       if (ok) tc_commit(bar_final);
     }
+   }
   } else if (warp < 8) {
+    setmaxnreg_inc<168>();
     // ------------------------------------------------------------------ P and dS (thread = key row)
     const int wg = warp >> 2;
     const int r = (warp & 3) * 32 + lane;
@@ -324,13 +329,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         tmem_ld32(t_s + cb, reinterpret_cast<uint32_t*>(pf));
         tmem_ld32(t_s + cb + 32, reinterpret_cast<uint32_t*>(pf) + 32);
         tc_wait_ld();
+        const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          const float4 l4 = ld_shared_f4(smem_lse + st * 512 + (cb + 4 * j) * 4);
-          float p0 = ex2_approx(fmaf(pf[4 * j + 0], p.scale_log2, -l4.x));
-          float p1 = ex2_approx(fmaf(pf[4 * j + 1], p.scale_log2, -l4.y));
-          float p2 = ex2_approx(fmaf(pf[4 * j + 2], p.scale_log2, -l4.z));
-          float p3 = ex2_approx(fmaf(pf[4 * j + 3], p.scale_log2, -l4.w));
+          const float4 l4 = ld_shared_f4(smem_lse + st * 512 + (cb + 4 * j) * 4);  // -lse * log2(e)
+          const float2 x01 = __ffma2_rn(make_float2(pf[4 * j + 0], pf[4 * j + 1]), scale2, make_float2(l4.x, l4.y));
+          const float2 x23 = __ffma2_rn(make_float2(pf[4 * j + 2], pf[4 * j + 3]), scale2, make_float2(l4.z, l4.w));
+          float p0 = ex2_approx(x01.x), p1 = ex2_approx(x01.y), p2 = ex2_approx(x23.x), p3 = ex2_approx(x23.y);
           if (masked) {
             const int q = cb + 4 * j;
             p0 = (q + 0 >= qlo && q + 0 < qhi) ? p0 : 0.f;
@@ -370,9 +375,12 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
               const int i = 8 * j + 4 * e;  // column within this half
-              const float4 d4 = ld_shared_f4(smem_dpsum + st * 512 + (cb + 32 * h + i) * 4);
-              float s0 = pf[32 * h + i + 0] * (dp[i + 0] - d4.x), s1 = pf[32 * h + i + 1] * (dp[i + 1] - d4.y);
-              float s2 = pf[32 * h + i + 2] * (dp[i + 2] - d4.z), s3 = pf[32 * h + i + 3] * (dp[i + 3] - d4.w);
+              const float4 d4 = ld_shared_f4(smem_dpsum + st * 512 + (cb + 32 * h + i) * 4);  // -sum_d O dO
+              const float2 s01 = __fmul2_rn(make_float2(pf[32 * h + i + 0], pf[32 * h + i + 1]),
+                                            __fadd2_rn(make_float2(dp[i + 0], dp[i + 1]), make_float2(d4.x, d4.y)));
+              const float2 s23 = __fmul2_rn(make_float2(pf[32 * h + i + 2], pf[32 * h + i + 3]),
+                                            __fadd2_rn(make_float2(dp[i + 2], dp[i + 3]), make_float2(d4.z, d4.w)));
+              float s0 = s01.x, s1 = s01.y, s2 = s23.x, s3 = s23.y;
               if (masked) {
                 const int q = cb + 32 * h + i;
                 s0 = (q + 0 >= qlo && q + 0 < qhi) ? s0 : 0.f;
@@ -431,6 +439,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       }
     }
   } else {
+    setmaxnreg_dec<96>();
     // ------------------------------------------------------------------ dQ drain (warps 8-11, thread = query row)
     const int r = (warp & 3) * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -507,7 +516,7 @@ __device__ __forceinline__ bool locate_row(const RowMap& m, int64_t row, int* ba
   return true;
 }
 
-// One warp per (row, head): dpsum = sum_d O dO, lse_log2 = lse log2(e) (+inf when lse = -inf), dq_accum row = 0.
+// One warp per (row, head): dpsum = -sum_d O dO, lse_log2 = -lse log2(e), dq_accum row = 0.
 template <int D>
 __global__ void __launch_bounds__(256) bwd_preprocess_kernel(
     const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout, const float* __restrict__ lse,
@@ -540,8 +549,8 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(
   const int64_t stat = (int64_t)head * map.rows + row;
   if (lane == 0) {
     const float value = lse[batch_coord * lse_bs + (int64_t)head * lse_hs + tensor_row];
-    lse_log2[stat] = value == -INFINITY ? INFINITY : value * kLog2e;
-    dpsum[stat] = sum;
+    lse_log2[stat] = value == -INFINITY ? -INFINITY : -value * kLog2e;  // rows without keys: exp2(x + -inf) = 0
+    dpsum[stat] = -sum;
   }
   float* acc = dq_accum + stat * D + lane * kPerLane;
   if constexpr (kPerLane == 4) {
