@@ -103,6 +103,12 @@ int b200fa_bwd(const b200fa_bwd_args* args, void* stream);
  * main kernel, after the postprocess kernel -- so a benchmark can time the main kernel by itself. NULL clears it. */
 int b200fa_bwd_timing_events(void* const* events);
 
+/* Tuning hook (no counterpart in the reference): `counters` is a device buffer of 32 int64 that the backward main
+ * kernel adds cycle counts to -- slots 0-10 = cycles its warps spent in each of its waits, 11 = cycles per CTA,
+ * 12 = iterations. NULL (the default) turns tracing off. Only libraries built with -DB200FA_TRACE count; the regular
+ * build accepts the call and records nothing. */
+int b200fa_set_trace(void* counters);
+
 /* Replaces inter_sequence.prepare_metadata (reference src/zigfa/_impl/inter_sequence.py:223-254).
  * Outputs: bits_t (n, ceil(n/32)) int32, cu_visible_k (n + 1) int32, cu_visible_q (n + 1) int32 (saturating). */
 int b200fa_interseq_metadata(const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, const int32_t* visibility_bits,

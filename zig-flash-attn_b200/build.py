@@ -27,6 +27,8 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr",
     "-Xptxas", "-v",
 ]
+if os.environ.get("B200FA_TRACE"):  # tuning build: cycle counters in the backward kernel (see b200fa_set_trace)
+    NVCC_FLAGS.append("-DB200FA_TRACE")
 
 
 def nvcc() -> str:

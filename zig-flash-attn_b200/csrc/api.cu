@@ -103,6 +103,9 @@ int* device_status_word() {
   return static_cast<int*>(address);
 }
 
+static long long* g_trace = nullptr;
+long long* trace_buffer() { return g_trace; }
+
 int launch_fwd(const b200fa_fwd_args& args, cudaStream_t stream);
 int launch_bwd(const b200fa_bwd_args& args, cudaStream_t stream);
 size_t bwd_workspace_bytes(const b200fa_problem& problem);
@@ -167,6 +170,11 @@ int b200fa_fwd(const b200fa_fwd_args* args, void* stream) {
   B200FA_REQUIRE(args->q && args->out && args->softmax_lse, "null tensor pointer");
   B200FA_REQUIRE(p.seqlen_k == 0 || (args->k && args->v), "null tensor pointer");
   return launch_fwd(*args, static_cast<cudaStream_t>(stream));
+}
+
+int b200fa_set_trace(void* counters) {
+  g_trace = static_cast<long long*>(counters);
+  return B200FA_OK;
 }
 
 int b200fa_bwd_timing_events(void* const* events) {

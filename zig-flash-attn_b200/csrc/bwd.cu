@@ -35,6 +35,7 @@ struct BwdParams {
   int64_t dv_batch_stride, dv_row_stride, dv_head_stride;
   const int2* work_list;  // packed problems: (key sequence, key block) per blockIdx.x
   int* status;
+  long long* trace;  // optional cycle counters, null = off
 };
 
 template <int D>
@@ -118,7 +119,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   const uint32_t tmem_slot = bars + 112, abort_slot = bars + 116;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + (abort_slot - smem_u32(smem_raw)));
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
-  const WaitCtx wctx{abort_flag, p.status};
+  const WaitCtx wctx{abort_flag, p.status, p.trace};
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -150,6 +151,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
+  const long long trace_start = trace_clock(WaitCtx{nullptr, nullptr, p.trace});
   // Query blocks per head (the same for every head of the group).
   int blocks_per_head = 0;
   {
@@ -189,7 +191,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       while (cur.next(&qb)) {
         const int st = it & 1;
         const int64_t row0 = stat_base + qb.row;
-        if (!mbar_wait_warp(bar_q_empty + 8 * st, ((it >> 1) & 1) ^ 1, wctx, kWaitBwdLoad)) { ok = false; break; }
+        if (!mbar_wait_traced(bar_q_empty + 8 * st, ((it >> 1) & 1) ^ 1, wctx, kWaitBwdLoad, 0, true)) { ok = false; break; }
         if (lane == 0) {
           mbar_expect_tx(bar_q_full + 8 * st, Cfg::kTileBytes);
 #pragma unroll
@@ -203,7 +205,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           if (row0 + r < p.rows) cp_async_4(smem_lse + st * 512 + r * 4, lse_head + row0 + r);
         }
         cp_async_arrive_noinc(bar_q_full + 8 * st);
-        if (!mbar_wait_warp(bar_do_empty, (it & 1) ^ 1, wctx, kWaitBwdLoad)) { ok = false; break; }
+        if (!mbar_wait_traced(bar_do_empty, (it & 1) ^ 1, wctx, kWaitBwdLoad, 1, true)) { ok = false; break; }
         if (lane == 0) {
           mbar_expect_tx(bar_do_full, Cfg::kTileBytes);
 #pragma unroll
@@ -252,7 +254,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         const uint32_t q_tile = smem_q + st * Cfg::kTileBytes;
         const bool more = it + 1 < iterations;
         // dV += P^T dO
-        if (!mbar_wait(bar_p_full, it & 1, wctx, kWaitBwdMma)) { ok = false; break; }
+        if (!mbar_wait_traced(bar_p_full, it & 1, wctx, kWaitBwdMma, 2, false)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
@@ -261,13 +263,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         tc_commit(bar_do_empty);
         // S^T of the next iteration
         if (more) {
-          if (!mbar_wait(bar_q_full + 8 * (st ^ 1), ((it + 1) >> 1) & 1, wctx, kWaitBwdMma)) { ok = false; break; }
+          if (!mbar_wait_traced(bar_q_full + 8 * (st ^ 1), ((it + 1) >> 1) & 1, wctx, kWaitBwdMma, 3, false)) { ok = false; break; }
           tc_fence_after();
           mma_kmajor(t_s, smem_k, smem_q + (st ^ 1) * Cfg::kTileBytes);
           tc_commit(bar_s_full);
         }
         // dK += dS^T Q ; dQ = dS K
-        if (!mbar_wait(bar_ds_full, it & 1, wctx, kWaitBwdMma)) { ok = false; break; }
+        if (!mbar_wait_traced(bar_ds_full, it & 1, wctx, kWaitBwdMma, 4, false)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
@@ -283,8 +285,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         tc_commit(bar_dq_full);
         // dP^T of the next iteration (its TMEM columns hold dQ until the reduce warps have drained it)
         if (more) {
-          if (!mbar_wait(bar_do_full, (it + 1) & 1, wctx, kWaitBwdMma) ||
-              !mbar_wait(bar_dq_empty, it & 1, wctx, kWaitBwdMma)) { ok = false; break; }
+          if (!mbar_wait_traced(bar_do_full, (it + 1) & 1, wctx, kWaitBwdMma, 5, false) ||
+              !mbar_wait_traced(bar_dq_empty, it & 1, wctx, kWaitBwdMma, 6, false)) { ok = false; break; }
           tc_fence_after();
           mma_kmajor(t_dp, smem_v, smem_do);
           tc_commit(bar_dp_full);
@@ -323,8 +325,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         if (!key_valid) qhi = 0;
         const bool masked = __any_sync(0xffffffffu, qlo > cb || qhi < cb + 64);
         // ---- P^T (kept in FP32 registers for dS, stored to TMEM as BF16 for the dV MMA)
-        if (!mbar_wait_warp(bar_s_full, it & 1, wctx, kWaitBwdCompute)) { ok = false; break; }
+        if (!mbar_wait_traced(bar_s_full, it & 1, wctx, kWaitBwdCompute, 7, true)) { ok = false; break; }
         tc_fence_after();
+        const long long t_p = trace_clock(wctx);
         float pf[64];
         tmem_ld32(t_s + cb, reinterpret_cast<uint32_t*>(pf));
         tmem_ld32(t_s + cb + 32, reinterpret_cast<uint32_t*>(pf) + 32);
@@ -359,11 +362,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar_p_full);
+        trace_add(wctx, 13, trace_clock(wctx) - t_p);
         // ---- dS^T = P^T o (dP^T - D), written to shared memory as BF16
-        if (!mbar_wait_warp(bar_dp_full, it & 1, wctx, kWaitBwdCompute)) { ok = false; break; }
+        if (!mbar_wait_traced(bar_dp_full, it & 1, wctx, kWaitBwdCompute, 8, true)) { ok = false; break; }
         // The dS tile of the previous iteration must have been consumed by its dK and dQ MMAs.
-        if (it > 0 && !mbar_wait_warp(bar_dq_full, (it - 1) & 1, wctx, kWaitBwdCompute)) { ok = false; break; }
+        if (it > 0 && !mbar_wait_traced(bar_dq_full, (it - 1) & 1, wctx, kWaitBwdCompute, 9, true)) { ok = false; break; }
         tc_fence_after();
+        const long long t_ds = trace_clock(wctx);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           float dp[32];
@@ -397,6 +402,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         tc_fence_before();
         fence_proxy_async_smem();
         mbar_arrive(bar_ds_full);
+        trace_add(wctx, 14, trace_clock(wctx) - t_ds);
         ++it;
       }
     }
@@ -455,7 +461,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       OtherBlock qb;
       while (cur.next(&qb)) {
         const int row0 = (int)(stat_base + qb.row);
-        if (!mbar_wait_warp(bar_dq_full, it & 1, wctx, kWaitBwdReduce)) { ok = false; break; }
+        if (!mbar_wait_traced(bar_dq_full, it & 1, wctx, kWaitBwdReduce, 10, true)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int ch = 0; ch < D / 32; ++ch) {
@@ -495,6 +501,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   __syncthreads();
   tc_fence_after();
   if (warp == 12) tmem_dealloc(tmem_base, 512);
+  if (kTraceBuild && threadIdx.x == 0) {
+    trace_add(wctx, 11, trace_clock(wctx) - trace_start);
+    trace_add(wctx, 12, iterations);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------- pre / post process
@@ -717,6 +727,7 @@ static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
   p.work_list = nullptr;
   p.status = device_status_word();
   if (!p.status) return B200FA_ERR_CUDA;
+  p.trace = trace_buffer();
 
   dim3 grid;
   bool run_main = !no_keys;

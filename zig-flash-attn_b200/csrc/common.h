@@ -45,4 +45,7 @@ int device_sm_count(int* count);
 // Device address of the library's status word on the current device (null + error text on failure).
 int* device_status_word();
 
+// Device buffer of 32 cycle counters set with b200fa_set_trace (null = tracing off).
+long long* trace_buffer();
+
 }  // namespace b200fa

@@ -103,7 +103,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       reinterpret_cast<volatile int*>(smem_raw + (abort_slot - smem_u32(smem_raw)));
   volatile uint32_t* tmem_ptr_smem =
       reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
-  const WaitCtx wctx{abort_flag, p.status};
+  const WaitCtx wctx{abort_flag, p.status, nullptr};
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;

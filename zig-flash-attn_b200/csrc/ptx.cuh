@@ -17,6 +17,7 @@ namespace b200fa {
 struct WaitCtx {
   volatile int* abort_flag;
   int* status;
+  long long* trace;  // optional cycle counters (null = off): see b200fa_set_trace
 };
 
 enum WaitCode : int {
@@ -97,6 +98,33 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, Wa
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, ctx, code);
+}
+// Tuning builds (-DB200FA_TRACE) add the cycles spent in each wait to trace[slot] (lane 0 of a warp only); regular
+// builds compile the traced calls down to the plain waits.
+#ifdef B200FA_TRACE
+constexpr bool kTraceBuild = true;
+#else
+constexpr bool kTraceBuild = false;
+#endif
+__device__ __forceinline__ bool mbar_wait_traced(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int code, int slot,
+                                                 bool warp_uniform) {
+  if (!kTraceBuild || ctx.trace == nullptr) {
+    const bool done = mbar_wait(bar, parity, ctx, code);
+    return warp_uniform ? __all_sync(0xffffffffu, done) : done;
+  }
+  const long long start = clock64();
+  bool done = mbar_wait(bar, parity, ctx, code);
+  if (warp_uniform) done = __all_sync(0xffffffffu, done);
+  if ((threadIdx.x & 31) == 0 || !warp_uniform)
+    atomicAdd(reinterpret_cast<unsigned long long*>(ctx.trace + slot), static_cast<unsigned long long>(clock64() - start));
+  return done;
+}
+__device__ __forceinline__ long long trace_clock(const WaitCtx& ctx) {
+  return (kTraceBuild && ctx.trace != nullptr) ? clock64() : 0;
+}
+__device__ __forceinline__ void trace_add(const WaitCtx& ctx, int slot, long long cycles) {
+  if (kTraceBuild && ctx.trace != nullptr && (threadIdx.x & 31) == 0)
+    atomicAdd(reinterpret_cast<unsigned long long*>(ctx.trace + slot), static_cast<unsigned long long>(cycles));
 }
 // Same, with a warp-uniform result (for code that goes on to execute .sync.aligned instructions).
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int code) {
