@@ -74,6 +74,20 @@ size_t b200fa_fwd_workspace_bytes(const b200fa_problem* problem);
 /* Replaces forward.forward (reference src/zigfa/_impl/forward.py:118-265): out = softmax(scale q k^T + mask) v. */
 int b200fa_fwd(const b200fa_fwd_args* args, void* stream);
 
+/* Forward attention without a caller workspace (no counterpart in the reference, whose forward always takes the
+ * scratch tensors its op layer allocates). Meant for callers that must not allocate device memory around the call:
+ * code running under a fixed device-memory plan where every byte is assigned up front, or a host-language binding
+ * that owns only the input and output buffers and has no allocator to ask for a workspace. Same arguments and results as b200fa_fwd; `workspace` and
+ * `workspace_bytes` are ignored. The work list of a packed batch is kept in a 64 KiB array in device memory owned by
+ * the library (held by every GPU that loads it until the process exits), so the batch may need at most 8192 work-list
+ * entries, i.e. (total_q + 255 * batch) / 256 <= 8192; larger batches are rejected with B200FA_ERR_INVALID and a
+ * message. Fixed-length problems need no scratch and have no such limit. The call itself allocates and frees nothing.
+ * The first call on each device looks up the array's device address (a synchronous CUDA runtime query), so make that
+ * first call before any stream capture begins. All calls on a device share the one array: each call rewrites every
+ * entry it uses before its kernel reads them, nothing needs clearing, but two calls whose kernels can overlap on the
+ * GPU (different streams without ordering) race on it -- keep calls to this entry point stream-ordered per device. */
+int b200fa_fwd_noalloc(const b200fa_fwd_args* args, void* stream);
+
 typedef struct b200fa_bwd_args {
   b200fa_problem problem;
   const void* q;

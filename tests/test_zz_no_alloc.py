@@ -1,0 +1,71 @@
+"""The forward entry point that needs no caller workspace (b200fa_fwd_noalloc), called through the C ABI.
+
+Some users of the library cannot allocate device memory around an attention call: their memory is planned up front,
+or their binding owns nothing but the input and output tensors. For them the library keeps the work list of a packed
+batch in a small array of its own. These tests check that this path returns exactly what the regular entry point
+(b200fa_fwd with a caller workspace) returns, on two different batches in a row -- the second smaller than the first,
+so stale entries of the first call are still in the shared array -- and that a batch too large for the array is refused
+with a clear message. The file name sorts last so that a run that stops at the first failure has already run every
+other test.
+"""
+import ctypes
+import itertools
+
+import pytest
+import torch
+
+from zigfa._impl import lib
+
+pytestmark = pytest.mark.gpu
+
+
+def forward_arguments(q, k, v, cu_q, cu_k, window, workspace):
+    out = torch.full_like(q, float("nan"))
+    lse = torch.full((q.shape[1], q.shape[0]), float("nan"), device=q.device)
+    problem = lib.make_problem(q, k, cu_q, cu_k, q.shape[-1] ** -0.5, *window)
+    args = lib.FwdArgs(
+        problem=problem, q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), softmax_lse=lse.data_ptr(),
+        q_stride=lib.strides3(q, True), k_stride=lib.strides3(k, True), v_stride=lib.strides3(v, True),
+        out_stride=lib.strides3(out, True), lse_stride=lib.Stride2(0, lse.stride(0)),
+        workspace=None if workspace is None else workspace.data_ptr(),
+        workspace_bytes=0 if workspace is None else workspace.numel(),
+    )
+    return args, out, lse
+
+
+def run_both(lengths, heads_q, heads_kv, head_dim, window, seed):
+    library = lib.library()
+    stream = torch.cuda.current_stream().cuda_stream
+    torch.manual_seed(seed)
+    total = sum(lengths)
+    q = torch.randn(total, heads_q, head_dim, device="cuda", dtype=torch.bfloat16)
+    k, v = (torch.randn(total, heads_kv, head_dim, device="cuda", dtype=torch.bfloat16) for _ in range(2))
+    cu = torch.tensor([0, *itertools.accumulate(lengths)], dtype=torch.int32, device="cuda")
+    problem = lib.make_problem(q, k, cu, cu, head_dim**-0.5, *window)
+    workspace = torch.empty(max(library.b200fa_fwd_workspace_bytes(ctypes.byref(problem)), 1), dtype=torch.uint8, device="cuda")
+    regular, out_regular, lse_regular = forward_arguments(q, k, v, cu, cu, window, workspace)
+    assert library.b200fa_fwd(ctypes.byref(regular), stream) == 0, lib.last_error()
+    # no workspace at all: the pointer is null and the size zero
+    bare, out_bare, lse_bare = forward_arguments(q, k, v, cu, cu, window, None)
+    assert library.b200fa_fwd_noalloc(ctypes.byref(bare), stream) == 0, lib.last_error()
+    torch.cuda.synchronize()
+    assert not torch.isnan(out_regular).any()
+    # same kernels, same work list: the results are identical, not merely close
+    assert torch.equal(out_bare, out_regular)
+    assert torch.equal(lse_bare, lse_regular)
+
+
+def test_noalloc_forward_matches_the_regular_entry_point_twice_in_a_row():
+    run_both([700, 33, 0, 1500, 256, 911], 8, 2, 128, (-1, 0), seed=11)
+    run_both([120, 300], 4, 4, 64, (50, 10), seed=12)
+
+
+def test_noalloc_forward_refuses_batches_beyond_its_scratch():
+    library = lib.library()
+    # shape-only check on the host: 8193 sequences of one row need 8193 work-list entries, one more than the array holds
+    q = torch.empty(8193, 1, 128, device="cuda", dtype=torch.bfloat16)
+    cu = torch.arange(8194, dtype=torch.int32, device="cuda")
+    args, _, _ = forward_arguments(q, q, q, cu, cu, (-1, -1), None)
+    assert library.b200fa_fwd_noalloc(ctypes.byref(args), torch.cuda.current_stream().cuda_stream) == -1
+    assert "b200fa_fwd_noalloc" in lib.last_error() and "8192" in lib.last_error()
+    torch.cuda.synchronize()

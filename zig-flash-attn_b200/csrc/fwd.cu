@@ -534,3 +534,46 @@ int launch_fwd(const b200fa_fwd_args& a, cudaStream_t stream) {
 }
 
 }  // namespace b200fa
+
+// -------------------------------------------------------------------------------------------------- no-allocation entry
+// Forward attention for callers that cannot hand the library a workspace. The only scratch the forward pass needs is
+// the work list of a packed (varlen / inter-sequence) batch; here it lives in a fixed array in device memory that
+// belongs to the library. Every GPU that loads the library holds these 64 KiB until the process exits.
+namespace b200fa {
+constexpr int kStaticWorkListEntries = 8192;  // (sequence, block) pairs; one entry covers 256 query rows
+static __device__ __align__(256) int32_t g_static_work_list[2 * kStaticWorkListEntries];
+
+// Device address of the array on the current device. `g_static_work_list` as written in host code is only a host-side
+// handle for the symbol, so the address a kernel can use has to be asked for, once per device, with that device current.
+static int static_work_list(int32_t** address) {
+  static int32_t* cached[64] = {nullptr};
+  int device = 0;
+  B200FA_CUDA_CHECK(cudaGetDevice(&device));
+  B200FA_REQUIRE(device >= 0 && device < 64, "device index %d is out of range", device);
+  if (!cached[device]) {
+    int32_t* pointer = nullptr;
+    B200FA_CUDA_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&pointer), g_static_work_list));
+    cached[device] = pointer;
+  }
+  *address = cached[device];
+  return B200FA_OK;
+}
+}  // namespace b200fa
+
+extern "C" int b200fa_fwd_noalloc(const b200fa_fwd_args* args, void* stream) {
+  using namespace b200fa;
+  B200FA_REQUIRE(args != nullptr, "null arguments");
+  const b200fa_problem& problem = args->problem;
+  const size_t needed = b200fa_fwd_workspace_bytes(&problem);
+  B200FA_REQUIRE(needed <= sizeof(int32_t) * 2 * kStaticWorkListEntries,
+                 "b200fa_fwd_noalloc: the batch needs a work list of %zu bytes (%zu entries of 256 query rows) but the "
+                 "built-in scratch holds %zu bytes (%d entries); use b200fa_fwd with a caller-provided workspace",
+                 needed, needed / 8, sizeof(int32_t) * 2 * kStaticWorkListEntries, kStaticWorkListEntries);
+  int32_t* scratch = nullptr;
+  const int status = static_work_list(&scratch);
+  if (status != B200FA_OK) return status;
+  b200fa_fwd_args with_scratch = *args;
+  with_scratch.workspace = scratch;
+  with_scratch.workspace_bytes = sizeof(int32_t) * 2 * kStaticWorkListEntries;
+  return b200fa_fwd(&with_scratch, stream);
+}

@@ -16,6 +16,7 @@ LIBRARY_PATH = Path(__file__).resolve().parent.parent / "libb200fa.so"
 EXPORTS = (
     "b200fa_fwd_workspace_bytes",
     "b200fa_fwd",
+    "b200fa_fwd_noalloc",
     "b200fa_bwd_workspace_bytes",
     "b200fa_bwd",
     "b200fa_bwd_timing_events",
@@ -120,6 +121,8 @@ def library() -> ctypes.CDLL:
     lib.b200fa_fwd_workspace_bytes.argtypes = [ctypes.POINTER(Problem)]
     lib.b200fa_fwd.restype = ctypes.c_int
     lib.b200fa_fwd.argtypes = [ctypes.POINTER(FwdArgs), ctypes.c_void_p]
+    lib.b200fa_fwd_noalloc.restype = ctypes.c_int
+    lib.b200fa_fwd_noalloc.argtypes = [ctypes.POINTER(FwdArgs), ctypes.c_void_p]
     lib.b200fa_bwd_workspace_bytes.restype = ctypes.c_size_t
     lib.b200fa_bwd_workspace_bytes.argtypes = [ctypes.POINTER(Problem)]
     lib.b200fa_bwd.restype = ctypes.c_int
