@@ -30,11 +30,12 @@ struct FwdParams {
   int m_blocks;           // fixed length: work items per (batch, head)
   int num_tiles;
   int* status;            // device status word of the library
+  long long* trace;       // optional cycle counters of tuning builds (slots 16-23), null = off
 };
 
 template <int D>
 struct FwdConfig {
-  static constexpr int kStages = D <= 64 ? 6 : 4;             // K/V ring slots
+  static constexpr int kStages = D <= 64 ? 8 : 4;             // K/V ring slots
   static constexpr int kTileBytes = kBlockM * D * 2;           // one 128 x D BF16 tile
   static constexpr int kHalves = D / 64;                       // 64-column (128-byte) swizzle panels per tile
   static constexpr int kPanelBytes = kBlockM * 128;
@@ -63,11 +64,16 @@ __device__ __forceinline__ FwdTile decode_tile(const FwdParams& p, int tile) {
     t.m0 = e.y * kFwdTileM;
     t.valid = e.x < pr.batch;
   } else {
-    int per_block = pr.batch * pr.heads_q;
-    int mb = tile / per_block;
-    int rem = tile - mb * per_block;
-    t.seq = rem / pr.heads_q;
-    t.head = rem - t.seq * pr.heads_q;
+    // Work items that run at the same time share K and V: all query blocks and query heads of one (batch entry, key
+    // head) are consecutive, late (heavy under a causal mask) query blocks first, so the K/V stream they read stays
+    // in L2 (reference zig/tile_scheduler.zig:516-669 orders tiles in L2-sized sections for the same reason).
+    const int group = pr.heads_q / pr.heads_kv;
+    const int per_group = p.m_blocks * group;
+    const int kv_group = tile / per_group;  // (batch entry, key head)
+    const int rem = tile - kv_group * per_group;
+    const int mb = rem / group;
+    t.seq = kv_group / pr.heads_kv;
+    t.head = (kv_group - t.seq * pr.heads_kv) * group + (rem - mb * group);
     t.m0 = (p.m_blocks - 1 - mb) * kFwdTileM;
     t.valid = true;
   }
@@ -84,6 +90,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   constexpr int NS = Cfg::kStages;
   // Register split between the warpgroups: 2 x 128 x 200 + 128 x 96 = 63488 of 65536.
   constexpr int kRegsSoftmax = 200, kRegsOther = 96;
+  // Of every kPolyPeriod pairs of scores, kPolyCount take the polynomial exp2 and the rest the MUFU.
+  constexpr int kPolyPeriod = 4, kPolyCount = 0;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t smem_q = smem_base;
@@ -103,7 +111,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       reinterpret_cast<volatile int*>(smem_raw + (abort_slot - smem_u32(smem_raw)));
   volatile uint32_t* tmem_ptr_smem =
       reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
-  const WaitCtx wctx{abort_flag, p.status, nullptr};
+  const WaitCtx wctx{abort_flag, p.status, p.trace};
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -203,7 +211,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         }
       };
       auto wait_kv = [&](uint32_t index) -> bool {
-        return mbar_wait(bar_kv_full + 8 * (index % NS), (index / NS) & 1, wctx, kWaitKvFull);
+        return mbar_wait_traced(bar_kv_full + 8 * (index % NS), (index / NS) & 1, wctx, kWaitKvFull, 16, false);
       };
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
         FwdTile t = decode_tile(p, tile);
@@ -236,7 +244,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           const uint32_t v_smem = smem_kv + (v_index % NS) * Cfg::kTileBytes;
           const uint32_t k_smem = smem_kv + (k_index % NS) * Cfg::kTileBytes;
           const uint32_t phase = blocks & 1;
-          if (!mbar_wait(bar_p_full, phase, wctx, kWaitPFull)) { ok = false; break; }
+          if (!mbar_wait_traced(bar_p_full, phase, wctx, kWaitPFull, 17, false)) { ok = false; break; }
           tc_fence_after();
           issue_pv(0, v_smem, !first);
           tc_commit(bar_pv_done);
@@ -244,7 +252,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             issue_s(0, k_smem);
             tc_commit(bar_s_full);
           }
-          if (!mbar_wait(bar_p_full + 8, phase, wctx, kWaitPFull)) { ok = false; break; }
+          if (!mbar_wait_traced(bar_p_full + 8, phase, wctx, kWaitPFull, 18, false)) { ok = false; break; }
           tc_fence_after();
           issue_pv(1, v_smem, !first);
           tc_commit(bar_pv_done + 8);
@@ -290,7 +298,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       int tile_blocks = 0;
       OtherBlock kb;
       while (cur.next(&kb)) {
-        if (!mbar_wait_warp(my_s_full, blocks & 1, wctx, kWaitSFull)) { ok = false; break; }
+        if (!mbar_wait_traced(my_s_full, blocks & 1, wctx, kWaitSFull, 19, true)) { ok = false; break; }
+        const long long t_soft = trace_clock(wctx);
         tc_fence_after();
         // Column limits of this row inside the block; `masked` is uniform over the warp.
         int lo, hi;
@@ -371,8 +380,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             for (int i = 0; i < 16; ++i) {
               const float2 x = __ffma2_rn(values[16 * c + i], scale2, shift2);
               float2 e;
-              e.x = ex2_approx(x.x);
-              e.y = ex2_approx(x.y);
+              if ((i % kPolyPeriod) < kPolyCount) {  // this share of the pairs is exponentiated on the FMA pipe
+                e = ex2_poly2(x);
+              } else {
+                e.x = ex2_approx(x.x);
+                e.y = ex2_approx(x.y);
+              }
               if (i & 1) sum_b = __fadd2_rn(sum_b, e); else sum_a = __fadd2_rn(sum_a, e);
               packed[i] = pack_bf16x2(e.x, e.y);
             }
@@ -390,6 +403,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(my_p_full);
+        trace_add(wctx, 20, trace_clock(wctx) - t_soft);
+        trace_add(wctx, 21, 1);
         ++blocks;
         ++tile_blocks;
       }
@@ -408,7 +423,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         }
         continue;
       }
-      if (!mbar_wait_warp(my_pv_done, (blocks - 1) & 1, wctx, kWaitEpilogue)) { ok = false; break; }
+      if (!mbar_wait_traced(my_pv_done, (blocks - 1) & 1, wctx, kWaitEpilogue, 22, true)) { ok = false; break; }
+      const long long t_epi = trace_clock(wctx);
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
@@ -433,6 +449,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         *lse_ptr = l > 0.f ? (mc + log2f(l)) * 0.69314718055994531f : -INFINITY;
       }
       tc_fence_before();
+      trace_add(wctx, 23, trace_clock(wctx) - t_epi);
+      trace_add(wctx, 24, 1);
     }
   }
 
@@ -468,6 +486,7 @@ static int launch_fwd_d(const b200fa_fwd_args& a, cudaStream_t stream) {
   p.m_blocks = 0;
   p.status = device_status_word();
   if (!p.status) return B200FA_ERR_CUDA;
+  p.trace = trace_buffer();
 
   const int64_t rows_q = bp.seqlen_q, rows_k = bp.seqlen_k;
   const int64_t tensor_batch = packed ? 1 : bp.batch;

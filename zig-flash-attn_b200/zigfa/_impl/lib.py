@@ -11,7 +11,10 @@ import ctypes
 import functools
 from pathlib import Path
 
-LIBRARY_PATH = Path(__file__).resolve().parent.parent / "libb200fa.so"
+import os
+
+# B200FA_LIBRARY points at another build of the library (tuning builds); the default is the one next to the package.
+LIBRARY_PATH = Path(os.environ.get("B200FA_LIBRARY") or Path(__file__).resolve().parent.parent / "libb200fa.so")
 
 EXPORTS = (
     "b200fa_fwd_workspace_bytes",
