@@ -137,8 +137,8 @@ const char* b200fa_last_error(void) { return g_error; }
 int b200fa_version(void) { return 100; }
 
 int b200fa_supports_head_dim(int32_t head_dim, int32_t direction) {
-  (void)direction;
-  return head_dim == 64 || head_dim == 128;
+  if (head_dim == 64 || head_dim == 128) return 1;
+  return head_dim == 256 && direction == 0;  // head_dim 256: forward only
 }
 
 int b200fa_device_status(void) {
@@ -151,7 +151,9 @@ int b200fa_device_status(void) {
 
 size_t b200fa_fwd_workspace_bytes(const b200fa_problem* p) {
   if (!p->cu_seqlens_q) return 0;
-  return static_cast<size_t>(work_list_entries(p->seqlen_q, p->batch, kFwdTileM)) * 8;
+  // work items are 256 query rows, 128 for head_dim 256
+  const int tile_rows = p->head_dim >= 256 ? kBlockM : kFwdTileM;
+  return static_cast<size_t>(work_list_entries(p->seqlen_q, p->batch, tile_rows)) * 8;
 }
 
 int b200fa_fwd(const b200fa_fwd_args* args, void* stream) {

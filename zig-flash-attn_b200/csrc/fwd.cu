@@ -14,24 +14,9 @@
 // Softmax runs in the log2 domain with a lazy rescale: the running reference maximum only moves when the block
 // maximum exceeds it by more than 8 (in log2 units), so O is almost never rescaled (reference
 // zig/flash_fwd_sm100.zig:963-976).
-#include "common.h"
-#include "ptx.cuh"
+#include "fwd_common.cuh"
 
 namespace b200fa {
-
-struct FwdParams {
-  Problem prob;
-  float scale_log2;
-  __nv_bfloat16* o;
-  int64_t o_batch_stride, o_row_stride, o_head_stride;
-  float* lse;
-  int64_t lse_batch_stride, lse_head_stride;
-  const int2* work_list;  // packed problems: (sequence, block) per entry; null for fixed length
-  int m_blocks;           // fixed length: work items per (batch, head)
-  int num_tiles;
-  int* status;            // device status word of the library
-  long long* trace;       // optional cycle counters of tuning builds (slots 16-23), null = off
-};
 
 template <int D>
 struct FwdConfig {
@@ -46,41 +31,6 @@ struct FwdConfig {
   static constexpr int kTmemS = 0;
   static constexpr int kTmemO = 256;
 };
-
-struct FwdTile {
-  int seq, head, kv_head, m0;
-  SeqInfo s;
-  bool valid;
-};
-
-__device__ __forceinline__ FwdTile decode_tile(const FwdParams& p, int tile) {
-  FwdTile t;
-  const Problem& pr = p.prob;
-  if (p.work_list) {
-    int entry = tile / pr.heads_q;
-    t.head = tile - entry * pr.heads_q;
-    int2 e = p.work_list[entry];
-    t.seq = e.x;
-    t.m0 = e.y * kFwdTileM;
-    t.valid = e.x < pr.batch;
-  } else {
-    // Work items that run at the same time share K and V: all query blocks and query heads of one (batch entry, key
-    // head) are consecutive, late (heavy under a causal mask) query blocks first, so the K/V stream they read stays
-    // in L2 (reference zig/tile_scheduler.zig:516-669 orders tiles in L2-sized sections for the same reason).
-    const int group = pr.heads_q / pr.heads_kv;
-    const int per_group = p.m_blocks * group;
-    const int kv_group = tile / per_group;  // (batch entry, key head)
-    const int rem = tile - kv_group * per_group;
-    const int mb = rem / group;
-    t.seq = kv_group / pr.heads_kv;
-    t.head = (kv_group - t.seq * pr.heads_kv) * group + (rem - mb * group);
-    t.m0 = (p.m_blocks - 1 - mb) * kFwdTileM;
-    t.valid = true;
-  }
-  t.kv_head = t.head / (pr.heads_q / pr.heads_kv);
-  if (t.valid) t.s = seq_info(pr, t.seq);
-  return t;
-}
 
 template <int D>
 __global__ void __launch_bounds__(FwdConfig<D>::kThreads, 1)
@@ -467,12 +417,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 
 // -------------------------------------------------------------------------------------------------- host side
 
-template <int D>
-static int launch_fwd_d(const b200fa_fwd_args& a, cudaStream_t stream) {
-  using Cfg = FwdConfig<D>;
+int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim, int tile_rows, int kv_box_rows,
+                    FwdParams* params, CUtensorMap* map_q, CUtensorMap* map_k, CUtensorMap* map_v, bool* nothing_to_do) {
+  const int D = head_dim;
   const b200fa_problem& bp = a.problem;
   const bool packed = bp.cu_seqlens_q != nullptr;
-  FwdParams p;
+  FwdParams& p = *params;
+  *nothing_to_do = true;
   p.prob = to_problem(bp);
   p.scale_log2 = bp.softmax_scale * 1.4426950408889634f;
   p.o = static_cast<__nv_bfloat16*>(a.out);
@@ -491,24 +442,23 @@ static int launch_fwd_d(const b200fa_fwd_args& a, cudaStream_t stream) {
   const int64_t rows_q = bp.seqlen_q, rows_k = bp.seqlen_k;
   const int64_t tensor_batch = packed ? 1 : bp.batch;
   if (packed) {
-    const int64_t entries = work_list_entries(rows_q, bp.batch, kFwdTileM);
+    const int64_t entries = work_list_entries(rows_q, bp.batch, tile_rows);
     B200FA_REQUIRE(a.workspace_bytes >= b200fa_fwd_workspace_bytes(&bp) && (entries == 0 || a.workspace),
                    "forward workspace is too small: need %zu bytes", b200fa_fwd_workspace_bytes(&bp));
     if (entries == 0) return B200FA_OK;
     const int32_t* other = bp.cu_visible_k ? bp.cu_visible_k : bp.cu_seqlens_k;
-    int status = b200fa_work_list(bp.cu_seqlens_q, other, bp.batch, kFwdTileM, 1, (int32_t)entries,
+    int status = b200fa_work_list(bp.cu_seqlens_q, other, bp.batch, tile_rows, 1, (int32_t)entries,
                                   static_cast<int32_t*>(a.workspace), stream);
     if (status != B200FA_OK) return status;
     p.work_list = static_cast<const int2*>(a.workspace);
     p.num_tiles = (int)(entries * bp.heads_q);
   } else {
-    p.m_blocks = ceil_div(bp.seqlen_q, kFwdTileM);
+    p.m_blocks = ceil_div(bp.seqlen_q, tile_rows);
     p.num_tiles = p.m_blocks * bp.batch * bp.heads_q;
   }
   if (p.num_tiles <= 0 || rows_q == 0) return B200FA_OK;
 
-  CUtensorMap map_q, map_k, map_v;
-  int status = encode_tensor_map(&map_q, a.q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, bp.heads_q, rows_q, tensor_batch,
+  int status = encode_tensor_map(map_q, a.q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, bp.heads_q, rows_q, tensor_batch,
                                  a.q_stride[2], a.q_stride[1], packed ? rows_q * a.q_stride[1] : a.q_stride[0], 64,
                                  kBlockM);
   if (status != B200FA_OK) return status;
@@ -517,15 +467,26 @@ static int launch_fwd_d(const b200fa_fwd_args& a, cudaStream_t stream) {
   const void* k_base = no_keys ? a.q : a.k;
   const void* v_base = no_keys ? a.q : a.v;
   const int64_t k_rows = no_keys ? 1 : rows_k;
-  status = encode_tensor_map(&map_k, k_base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, no_keys ? 1 : bp.heads_kv, k_rows,
+  status = encode_tensor_map(map_k, k_base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, no_keys ? 1 : bp.heads_kv, k_rows,
                              tensor_batch, no_keys ? D : a.k_stride[2], no_keys ? D : a.k_stride[1],
-                             no_keys ? D : (packed ? k_rows * a.k_stride[1] : a.k_stride[0]), 64, kBlockN);
+                             no_keys ? D : (packed ? k_rows * a.k_stride[1] : a.k_stride[0]), 64, kv_box_rows);
   if (status != B200FA_OK) return status;
-  status = encode_tensor_map(&map_v, v_base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, no_keys ? 1 : bp.heads_kv, k_rows,
+  status = encode_tensor_map(map_v, v_base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, no_keys ? 1 : bp.heads_kv, k_rows,
                              tensor_batch, no_keys ? D : a.v_stride[2], no_keys ? D : a.v_stride[1],
-                             no_keys ? D : (packed ? k_rows * a.v_stride[1] : a.v_stride[0]), 64, kBlockN);
+                             no_keys ? D : (packed ? k_rows * a.v_stride[1] : a.v_stride[0]), 64, kv_box_rows);
   if (status != B200FA_OK) return status;
+  *nothing_to_do = false;
+  return B200FA_OK;
+}
 
+template <int D>
+static int launch_fwd_d(const b200fa_fwd_args& a, cudaStream_t stream) {
+  using Cfg = FwdConfig<D>;
+  FwdParams p;
+  CUtensorMap map_q, map_k, map_v;
+  bool nothing_to_do = false;
+  int status = prepare_forward(a, stream, D, kFwdTileM, kBlockN, &p, &map_q, &map_k, &map_v, &nothing_to_do);
+  if (status != B200FA_OK || nothing_to_do) return status;
   static bool attribute_set = false;
   if (!attribute_set) {
     B200FA_CUDA_CHECK(cudaFuncSetAttribute(fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
@@ -546,8 +507,10 @@ int launch_fwd(const b200fa_fwd_args& a, cudaStream_t stream) {
       return launch_fwd_d<64>(a, stream);
     case 128:
       return launch_fwd_d<128>(a, stream);
+    case 256:
+      return launch_fwd_256(a, stream);
     default:
-      set_error("head_dim %d is not supported by the forward kernel (supported: 64, 128)", a.problem.head_dim);
+      set_error("head_dim %d is not supported by the forward kernel (supported: 64, 128, 256)", a.problem.head_dim);
       return B200FA_ERR_UNSUPPORTED;
   }
 }
