@@ -38,10 +38,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
            const __grid_constant__ CUtensorMap map_v, const __grid_constant__ FwdParams p) {
   using Cfg = FwdConfig<D>;
   constexpr int NS = Cfg::kStages;
-  // Register split between the warpgroups: 2 x 128 x 200 + 128 x 96 = 63488 of 65536.
-  constexpr int kRegsSoftmax = 200, kRegsOther = 96;
+  // Register split between the warpgroups: 2 x 128 x 208 + 128 x 88 = 64512, the 384 x 168 registers the CTA is launched with (setmaxnreg only moves registers inside that pool).
+  constexpr int kRegsSoftmax = 208, kRegsOther = 88;
   // Of every kPolyPeriod pairs of scores, kPolyCount take the polynomial exp2 and the rest the MUFU.
   constexpr int kPolyPeriod = 4, kPolyCount = 0;
+  // Keep all 128 scores of a row in registers (true) or read the lower half from TMEM a second time (false).
+  constexpr bool kSinglePass = false;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t smem_q = smem_base;
@@ -342,13 +344,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             tmem_st16(t_s + 64 + first_p_column + 16 * c, packed);
           }
         };
-        // Pass 2 for columns [0,64): the loads are in flight while the upper half is exponentiated.
-        tmem_ld32(t_s, reinterpret_cast<uint32_t*>(low));
-        tmem_ld32(t_s + 32, reinterpret_cast<uint32_t*>(low) + 32);
-        exponentiate(high, 32);
-        tc_wait_ld();
-        if (masked) apply_mask(low, 0);
-        exponentiate(low, 0);
+        if (kSinglePass) {
+          exponentiate(high, 32);
+          exponentiate(low, 0);
+        } else {
+          // Pass 2 for columns [0,64): the loads are in flight while the upper half is exponentiated.
+          tmem_ld32(t_s, reinterpret_cast<uint32_t*>(low));
+          tmem_ld32(t_s + 32, reinterpret_cast<uint32_t*>(low) + 32);
+          exponentiate(high, 32);
+          tc_wait_ld();
+          if (masked) apply_mask(low, 0);
+          exponentiate(low, 0);
+        }
         l += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
         tc_wait_st();
         tc_fence_before();
