@@ -318,7 +318,10 @@ def main():
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "roofline": {"kernel": "bwd_kernel<128> (dK/dV/dQ main)", "bound": "tensor",
                          "achieved": flops_bwd / (ms_main * 1e-3) / 1e12, "peak": peaks["burst"], "unit": "TFLOP/s",
-                         "frac": flops_bwd / (ms_main * 1e-3) / 1e12 / peaks["burst"], "traffic": None,
+                         "frac": flops_bwd / (ms_main * 1e-3) / 1e12 / peaks["burst"],
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture on one batch entry of this
+                         # workload (profiles/bwd_kernel_d128_c1s.md: 429.7 MB), scaled by the batch entries per launch
+                         "traffic": 429.7e6 * batch if options.workload in ("c1", "c1s") else None,
                          "peak_source": f"{peaks['source']} cuBLAS BF16 burst", "sustained_peak": peaks["sustained"]},
             "roofline_fwd": {"kernel": "fwd_kernel<128>", "bound": "tensor", "achieved": flops_fwd / (ms_fwd * 1e-3) / 1e12,
                              "peak": peaks["burst"], "unit": "TFLOP/s",
