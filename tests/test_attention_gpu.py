@@ -15,7 +15,7 @@ from zigfa._impl import ops
 pytestmark = pytest.mark.gpu
 
 HEAD_LAYOUTS = {"mha": (6, 6), "mqa": (6, 1), "gqa": (6, 3)}
-HEAD_DIMS = (64, 128)
+HEAD_DIMS = (64, 72, 96, 128)
 SEQLENS = [
     (1, 1), (3, 3), (64, 32), (64, 128), (128, 128), (128, 192), (256, 256), (239, 1), (799, 3), (113, 203),
     (113, 128), (128, 217), (113, 211), (108, 256), (256, 512), (384, 256), (640, 128), (1024, 1024), (1023, 1024),
@@ -136,7 +136,7 @@ VARLEN_SEQLENS = [(1, 1), (1, 3), (2, 1), (511, 1), (3, 513), (64, 128), (128, 1
 @pytest.mark.parametrize("zero_lengths", [False, True])
 def test_varlen_matches_oracle(kind, zero_lengths):
     for index, (max_q, max_k) in enumerate(VARLEN_SEQLENS):
-        head_dim = HEAD_DIMS[index % 2]
+        head_dim = HEAD_DIMS[index % len(HEAD_DIMS)]
         heads_q, heads_kv = list(HEAD_LAYOUTS.values())[index % 3]
         batch = 49 if max_q * max_k <= 64 * 128 else 7
         generator = torch.Generator().manual_seed(index)

@@ -29,6 +29,7 @@ struct BwdParams {
   const float* lse_log2;  // (heads_q, rows) : -lse * log2(e)
   const float* dpsum;     // (heads_q, rows) : -sum_d O * dO
   int64_t rows;           // rows of the statistics / dQ accumulator per head (batch * seqlen_q or total_q)
+  int head_dim;           // columns of the tensors (<= the compiled D; TMA zero-fills the columns in between)
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;
   int64_t dk_batch_stride, dk_row_stride, dk_head_stride;
@@ -434,7 +435,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
               v.y = pack_bf16x2(__uint_as_float(acc[8 * i + 2]) * mul, __uint_as_float(acc[8 * i + 3]) * mul);
               v.z = pack_bf16x2(__uint_as_float(acc[8 * i + 4]) * mul, __uint_as_float(acc[8 * i + 5]) * mul);
               v.w = pack_bf16x2(__uint_as_float(acc[8 * i + 6]) * mul, __uint_as_float(acc[8 * i + 7]) * mul);
-              dst[4 * ch + i] = v;
+              if (32 * ch + 8 * i < p.head_dim) dst[4 * ch + i] = v;
             }
           }
         }
@@ -509,6 +510,7 @@ struct RowMap {
   const int32_t* cu_q;  // null = fixed length
   int batch, seqlen_q;
   int64_t rows;  // batch * seqlen_q or total_q
+  int head_dim;  // columns of the tensors (the kernels are compiled for head_dim rounded up to 64 or 128)
 };
 // Maps a statistics row to (sequence, row within the sequence, batch coordinate, packed row).
 __device__ __forceinline__ bool locate_row(const RowMap& m, int64_t row, int* batch_coord, int64_t* tensor_row) {
@@ -540,7 +542,9 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(
   const __nv_bfloat16* o_ptr = o + batch_coord * o_bs + tensor_row * o_rs + (int64_t)head * o_hs + lane * kPerLane;
   const __nv_bfloat16* do_ptr = dout + batch_coord * do_bs + tensor_row * do_rs + (int64_t)head * do_hs + lane * kPerLane;
   float sum = 0.f;
-  if constexpr (kPerLane == 4) {
+  if (lane * kPerLane >= map.head_dim) {
+    // padding columns of a head_dim below the compiled one
+  } else if constexpr (kPerLane == 4) {
     const uint2 a = *reinterpret_cast<const uint2*>(o_ptr), b = *reinterpret_cast<const uint2*>(do_ptr);
     sum = __uint_as_float(a.x << 16) * __uint_as_float(b.x << 16) +
           __uint_as_float(a.x & 0xffff0000u) * __uint_as_float(b.x & 0xffff0000u) +
@@ -582,6 +586,7 @@ __global__ void __launch_bounds__(256) bwd_postprocess_kernel(const float* __res
   constexpr int kPerLane = D / 32;
   const float* acc = dq_accum + ((int64_t)head * map.rows + row) * D + lane * kPerLane;
   __nv_bfloat16* out = dq + batch_coord * dq_bs + tensor_row * dq_rs + (int64_t)head * dq_hs + lane * kPerLane;
+  if (lane * kPerLane >= map.head_dim) return;
   if constexpr (kPerLane == 4) {
     const float4 v = *reinterpret_cast<const float4*>(acc);
     uint2 packed;
@@ -619,7 +624,8 @@ static BwdWorkspace plan_workspace(const b200fa_problem& p) {
   w.lse_log2 = 0;
   w.dpsum = stat_bytes;
   w.dq_accum = 2 * stat_bytes;
-  const size_t acc_bytes = ((size_t)p.heads_q * w.rows * p.head_dim * 4 + 255) & ~size_t(255);
+  const int compiled_dim = p.head_dim <= 64 ? 64 : 128;  // the accumulator has the compiled width
+  const size_t acc_bytes = ((size_t)p.heads_q * w.rows * compiled_dim * 4 + 255) & ~size_t(255);
   w.work_list = w.dq_accum + acc_bytes;
   w.entries = packed ? work_list_entries(p.seqlen_k, p.batch, kBlockN) : 0;
   w.total = w.work_list + (size_t)w.entries * 8;
@@ -644,18 +650,18 @@ static int launch_main(const b200fa_bwd_args& a, const BwdParams& p, dim3 grid, 
   const void* do_base = no_queries ? a.k : a.dout;
   const int64_t q_rows = no_queries ? 1 : rows_q;
   const int64_t qh = no_queries ? 1 : bp.heads_q;
-  status = encode_tensor_map(&map_q, q_base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, qh, q_rows, tensor_batch,
+  status = encode_tensor_map(&map_q, q_base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, bp.head_dim, qh, q_rows, tensor_batch,
                              no_queries ? D : a.q_stride[2], no_queries ? D : a.q_stride[1],
                              no_queries ? D : (packed ? q_rows * a.q_stride[1] : a.q_stride[0]), 64, kBlockM);
   if (status != B200FA_OK) return status;
-  status = encode_tensor_map(&map_do, do_base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, qh, q_rows, tensor_batch,
+  status = encode_tensor_map(&map_do, do_base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, bp.head_dim, qh, q_rows, tensor_batch,
                              no_queries ? D : a.dout_stride[2], no_queries ? D : a.dout_stride[1],
                              no_queries ? D : (packed ? q_rows * a.dout_stride[1] : a.dout_stride[0]), 64, kBlockM);
   if (status != B200FA_OK) return status;
-  status = encode_tensor_map(&map_k, a.k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, bp.heads_kv, rows_k, tensor_batch,
+  status = encode_tensor_map(&map_k, a.k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, bp.head_dim, bp.heads_kv, rows_k, tensor_batch,
                              a.k_stride[2], a.k_stride[1], packed ? rows_k * a.k_stride[1] : a.k_stride[0], 64, kBlockN);
   if (status != B200FA_OK) return status;
-  status = encode_tensor_map(&map_v, a.v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, bp.heads_kv, rows_k, tensor_batch,
+  status = encode_tensor_map(&map_v, a.v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, bp.head_dim, bp.heads_kv, rows_k, tensor_batch,
                              a.v_stride[2], a.v_stride[1], packed ? rows_k * a.v_stride[1] : a.v_stride[0], 64, kBlockN);
   if (status != B200FA_OK) return status;
   if (no_queries) {
@@ -695,7 +701,7 @@ static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
   float* dq_accum = reinterpret_cast<float*>(ws + w.dq_accum);
   const int64_t tensor_batch = packed ? 1 : bp.batch;
 
-  RowMap map{bp.cu_seqlens_q, bp.batch, bp.seqlen_q, w.rows};
+  RowMap map{bp.cu_seqlens_q, bp.batch, bp.seqlen_q, w.rows, bp.head_dim};
   mark(0, stream);
   if (w.rows > 0) {
     dim3 grid((unsigned)((w.rows + 7) / 8), (unsigned)bp.heads_q);
@@ -713,6 +719,7 @@ static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
   p.lse_log2 = lse_log2;
   p.dpsum = dpsum;
   p.rows = w.rows;
+  p.head_dim = bp.head_dim;
   p.dk = static_cast<__nv_bfloat16*>(a.dk);
   p.dv = static_cast<__nv_bfloat16*>(a.dv);
   p.dk_batch_stride = packed ? 0 : a.dk_stride[0];
@@ -763,10 +770,12 @@ int launch_bwd(const b200fa_bwd_args& a, cudaStream_t stream) {
   switch (a.problem.head_dim) {
     case 64:
       return launch_bwd_d<64>(a, stream);
+    case 72:   // compiled for 128 columns; TMA zero-fills the missing ones and the epilogues skip them
+    case 96:
     case 128:
       return launch_bwd_d<128>(a, stream);
     default:
-      set_error("head_dim %d is not supported by the backward kernels (supported: 64, 128)", a.problem.head_dim);
+      set_error("head_dim %d is not supported by the backward kernels (supported: 64, 72, 96, 128)", a.problem.head_dim);
       return B200FA_ERR_UNSUPPORTED;
   }
 }

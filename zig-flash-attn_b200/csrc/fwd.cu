@@ -375,7 +375,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         if (row_valid) {
           const uint4 zero = make_uint4(0, 0, 0, 0);
 #pragma unroll
-          for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(o_row)[c] = zero;
+          for (int c = 0; c < D / 8; ++c)
+            if (8 * c < p.head_dim) reinterpret_cast<uint4*>(o_row)[c] = zero;
           *lse_ptr = -INFINITY;
         }
         continue;
@@ -397,7 +398,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             v.y = pack_bf16x2(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
             v.z = pack_bf16x2(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
             v.w = pack_bf16x2(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
-            reinterpret_cast<uint4*>(o_row)[4 * c + i] = v;
+            if (32 * c + 8 * i < p.head_dim) reinterpret_cast<uint4*>(o_row)[4 * c + i] = v;
           }
         }
       }
@@ -426,8 +427,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 
 int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim, int tile_rows, int kv_box_rows,
                     FwdParams* params, CUtensorMap* map_q, CUtensorMap* map_k, CUtensorMap* map_v, bool* nothing_to_do) {
-  const int D = head_dim;
   const b200fa_problem& bp = a.problem;
+  const int D = bp.head_dim;  // columns of the tensors; `head_dim` is the width the kernel is compiled for
+  (void)head_dim;
   const bool packed = bp.cu_seqlens_q != nullptr;
   FwdParams& p = *params;
   *nothing_to_do = true;
@@ -442,6 +444,7 @@ int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim,
   p.lse_head_stride = a.lse_stride[1];
   p.work_list = nullptr;
   p.m_blocks = 0;
+  p.head_dim = bp.head_dim;
   p.status = device_status_word();
   if (!p.status) return B200FA_ERR_CUDA;
   p.trace = trace_buffer();
@@ -512,12 +515,14 @@ int launch_fwd(const b200fa_fwd_args& a, cudaStream_t stream) {
   switch (a.problem.head_dim) {
     case 64:
       return launch_fwd_d<64>(a, stream);
+    case 72:   // compiled for 128 columns; TMA zero-fills the missing ones and the epilogue skips them
+    case 96:
     case 128:
       return launch_fwd_d<128>(a, stream);
     case 256:
       return launch_fwd_256(a, stream);
     default:
-      set_error("head_dim %d is not supported by the forward kernel (supported: 64, 128, 256)", a.problem.head_dim);
+      set_error("head_dim %d is not supported by the forward kernel (supported: 64, 72, 96, 128, 256)", a.problem.head_dim);
       return B200FA_ERR_UNSUPPORTED;
   }
 }

@@ -15,6 +15,7 @@ struct FwdParams {
   const int2* work_list;  // packed problems: (sequence, block) per entry; null for fixed length
   int m_blocks;           // fixed length: work items per (batch, head)
   int num_tiles;
+  int head_dim;           // columns of the tensors (<= the compiled width; TMA zero-fills the columns in between)
   int* status;            // device status word of the library
   long long* trace;       // optional cycle counters of tuning builds (slots 16-23), null = off
 };
