@@ -27,6 +27,7 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr",
     "-Xptxas", "-v",
 ]
+NVCC_FLAGS += os.environ.get("B200FA_NVCC_FLAGS", "").split()  # tuning builds: extra -D switches
 if os.environ.get("B200FA_TRACE"):  # tuning build: cycle counters in the backward kernel (see b200fa_set_trace)
     NVCC_FLAGS.append("-DB200FA_TRACE")
 

@@ -113,11 +113,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   const uint32_t bar_kv_full = bars, bar_q_full = bars + 8 /*[2]*/, bar_q_empty = bars + 24 /*[2]*/;
   const uint32_t bar_do_full = bars + 40, bar_do_empty = bars + 48, bar_s_full = bars + 56, bar_p_full = bars + 64;
   const uint32_t bar_dp_full = bars + 72, bar_ds_full = bars + 80, bar_dq_full = bars + 88, bar_dq_empty = bars + 96;
-  const uint32_t bar_final = bars + 104;
+  const uint32_t bar_final = bars + 104, bar_ds_empty = bars + 120;
   const uint32_t tmem_slot = bars + 112, abort_slot = bars + 116;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + (abort_slot - smem_u32(smem_raw)));
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
   const WaitCtx wctx{abort_flag, p.status, p.trace};
+  int trace_n = 0;
+  const bool traced_cta = kTraceBuild && blockIdx.x == 8 && blockIdx.y == 0 && blockIdx.z == 0;  // timeline of one CTA
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -138,6 +140,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     mbar_init(bar_dq_full, 1);
     mbar_init(bar_dq_empty, 128);
     mbar_init(bar_final, 1);
+    mbar_init(bar_ds_empty, 1);
     fence_barrier_init();
   }
   if (warp == 12) {
@@ -205,6 +208,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         cp_async_arrive_noinc(bar_q_full + 8 * st);
         if (!mbar_wait_traced(bar_do_empty, (it & 1) ^ 1, wctx, kWaitBwdLoad, 1, true)) { ok = false; break; }
         if (lane == 0) {
+          trace_event(wctx, traced_cta && it < 10, 3, trace_n, 1000 + it);  // dO load issued
           mbar_expect_tx(bar_do_full, Cfg::kTileBytes);
 #pragma unroll
           for (int h = 0; h < Cfg::kHalves; ++h)
@@ -259,35 +263,48 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           umma_ts(t_dv, t_s + (kk >> 2) * 64 + (kk & 3) * 8, umma_smem_desc(smem_do + kk * 2048, Cfg::kPanelBytes, 1024),
                   idesc_dv, it > 0 || kk > 0);
         tc_commit(bar_do_empty);
+        trace_event(wctx, traced_cta && it < 10, 0, trace_n, 100 + it);  // dV issued
         // S^T of the next iteration
         if (more) {
           if (!mbar_wait_traced(bar_q_full + 8 * (st ^ 1), ((it + 1) >> 1) & 1, wctx, kWaitBwdMma, 3, false)) { ok = false; break; }
           tc_fence_after();
           mma_kmajor(t_s, smem_k, smem_q + (st ^ 1) * Cfg::kTileBytes);
           tc_commit(bar_s_full);
+          trace_event(wctx, traced_cta && it < 10, 0, trace_n, 200 + it);  // S(it+1) issued
         }
         // dK += dS^T Q ; dQ = dS K
         if (!mbar_wait_traced(bar_ds_full, it & 1, wctx, kWaitBwdMma, 4, false)) { ok = false; break; }
         tc_fence_after();
+        auto issue_dq = [&]() {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t a_off = (kk >> 2) * Cfg::kPanelBytes + (kk & 3) * 32;
-          umma_ss(t_dk, umma_smem_desc(smem_ds + a_off, 16, 1024), umma_smem_desc(q_tile + kk * 2048, Cfg::kPanelBytes, 1024),
-                  idesc_dk, it > 0 || kk > 0);
-        }
-        tc_commit(bar_q_empty + 8 * st);
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ss(t_dp, umma_smem_desc(smem_ds + kk * 2048, Cfg::kPanelBytes, 1024),
+                    umma_smem_desc(smem_k + kk * 2048, Cfg::kPanelBytes, 1024), idesc_dq, kk > 0);
+          tc_commit(bar_dq_full);
+        };
+        auto issue_dk = [&]() {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_ss(t_dp, umma_smem_desc(smem_ds + kk * 2048, Cfg::kPanelBytes, 1024),
-                  umma_smem_desc(smem_k + kk * 2048, Cfg::kPanelBytes, 1024), idesc_dq, kk > 0);
-        tc_commit(bar_dq_full);
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t a_off = (kk >> 2) * Cfg::kPanelBytes + (kk & 3) * 32;
+            umma_ss(t_dk, umma_smem_desc(smem_ds + a_off, 16, 1024), umma_smem_desc(q_tile + kk * 2048, Cfg::kPanelBytes, 1024),
+                    idesc_dk, it > 0 || kk > 0);
+          }
+          tc_commit(bar_q_empty + 8 * st);
+        };
+        // dQ first: its drain is on the chain to the next dP^T (same TMEM columns); dK runs while the drain does.
+        issue_dq();
+        issue_dk();
+        tc_commit(bar_ds_empty);
+        trace_event(wctx, traced_cta && it < 10, 0, trace_n, 300 + it);  // dK, dQ issued
         // dP^T of the next iteration (its TMEM columns hold dQ until the reduce warps have drained it)
         if (more) {
           if (!mbar_wait_traced(bar_do_full, (it + 1) & 1, wctx, kWaitBwdMma, 5, false) ||
               !mbar_wait_traced(bar_dq_empty, it & 1, wctx, kWaitBwdMma, 6, false)) { ok = false; break; }
           tc_fence_after();
+          trace_event(wctx, traced_cta && it < 10, 0, trace_n, 350 + it);  // dO(it+1) and dQ drain ready
           mma_kmajor(t_dp, smem_v, smem_do);
           tc_commit(bar_dp_full);
+          trace_event(wctx, traced_cta && it < 10, 0, trace_n, 400 + it);  // dP(it+1) issued
         }
       }
       if (ok) tc_commit(bar_final);
@@ -326,6 +343,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         if (!mbar_wait_traced(bar_s_full, it & 1, wctx, kWaitBwdCompute, 7, true)) { ok = false; break; }
         tc_fence_after();
         const long long t_p = trace_clock(wctx);
+        trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 500 + it);  // S ready
         float pf[64];
         tmem_ld32(t_s + cb, reinterpret_cast<uint32_t*>(pf));
         tmem_ld32(t_s + cb + 32, reinterpret_cast<uint32_t*>(pf) + 32);
@@ -361,12 +379,14 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         tc_fence_before();
         mbar_arrive(bar_p_full);
         trace_add(wctx, 13, trace_clock(wctx) - t_p);
+        trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 600 + it);  // P stored
         // ---- dS^T = P^T o (dP^T - D), written to shared memory as BF16
         if (!mbar_wait_traced(bar_dp_full, it & 1, wctx, kWaitBwdCompute, 8, true)) { ok = false; break; }
         // The dS tile of the previous iteration must have been consumed by its dK and dQ MMAs.
-        if (it > 0 && !mbar_wait_traced(bar_dq_full, (it - 1) & 1, wctx, kWaitBwdCompute, 9, true)) { ok = false; break; }
+        if (it > 0 && !mbar_wait_traced(bar_ds_empty, (it - 1) & 1, wctx, kWaitBwdCompute, 9, true)) { ok = false; break; }
         tc_fence_after();
         const long long t_ds = trace_clock(wctx);
+        trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 700 + it);  // dP ready
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           float dp[32];
@@ -401,6 +421,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         fence_proxy_async_smem();
         mbar_arrive(bar_ds_full);
         trace_add(wctx, 14, trace_clock(wctx) - t_ds);
+        trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 800 + it);  // dS stored
         ++it;
       }
     }
@@ -469,6 +490,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           if (ch == D / 32 - 1) {
             tc_fence_before();
             mbar_arrive(bar_dq_empty);
+            trace_event(wctx, traced_cta && threadIdx.x == 256 && it < 10, 2, trace_n, 900 + it);  // dQ drained
           }
           const uint32_t stage = smem_stage + (chunks & 1) * Cfg::kStageBytes;
           if (leader) bulk_wait_group_read<1>();  // the copy that read this buffer two chunks ago is done with it

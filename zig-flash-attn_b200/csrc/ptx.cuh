@@ -122,6 +122,14 @@ __device__ __forceinline__ bool mbar_wait_traced(uint32_t bar, uint32_t parity, 
 __device__ __forceinline__ long long trace_clock(const WaitCtx& ctx) {
   return (kTraceBuild && ctx.trace != nullptr) ? clock64() : 0;
 }
+// Timeline events of one CTA (tuning builds): each role writes id << 48 | cycle counter into its own region
+// trace[64 + 720 * role + n]; plain stores, so the logging thread does not wait on memory.
+__device__ __forceinline__ void trace_event(const WaitCtx& ctx, bool selected, int role, int& n, int id) {
+  if (kTraceBuild && ctx.trace != nullptr && selected && n < 720) {
+    ctx.trace[64 + 720 * role + n] = (static_cast<long long>(id) << 48) | (clock64() & 0xffffffffffffll);
+    ++n;
+  }
+}
 __device__ __forceinline__ void trace_add(const WaitCtx& ctx, int slot, long long cycles) {
   if (kTraceBuild && ctx.trace != nullptr && (threadIdx.x & 31) == 0)
     atomicAdd(reinterpret_cast<unsigned long long*>(ctx.trace + slot), static_cast<unsigned long long>(cycles));
