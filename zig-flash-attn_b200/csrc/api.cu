@@ -137,8 +137,8 @@ const char* b200fa_last_error(void) { return g_error; }
 int b200fa_version(void) { return 100; }
 
 int b200fa_supports_head_dim(int32_t head_dim, int32_t direction) {
-  if (head_dim == 64 || head_dim == 72 || head_dim == 96 || head_dim == 128) return 1;
-  return head_dim == 256 && direction == 0;  // head_dim 256: forward only
+  (void)direction;  // every compiled head dimension has both a forward and a backward kernel
+  return head_dim == 64 || head_dim == 72 || head_dim == 96 || head_dim == 128 || head_dim == 256;
 }
 
 int b200fa_device_status(void) {

@@ -16,28 +16,9 @@
 // MMAs, warp 13 issues TMA loads and the asynchronous copies of the per-row statistics.
 #include <limits.h>
 
-#include "common.h"
-#include "ptx.cuh"
+#include "bwd_common.cuh"
 
 namespace b200fa {
-
-constexpr float kLog2e = 1.4426950408889634f;
-
-struct BwdParams {
-  Problem prob;
-  float scale, scale_log2;
-  const float* lse_log2;  // (heads_q, rows) : -lse * log2(e)
-  const float* dpsum;     // (heads_q, rows) : -sum_d O * dO
-  int64_t rows;           // rows of the statistics / dQ accumulator per head (batch * seqlen_q or total_q)
-  int head_dim;           // columns of the tensors (<= the compiled D; TMA zero-fills the columns in between)
-  __nv_bfloat16* dk;
-  __nv_bfloat16* dv;
-  int64_t dk_batch_stride, dk_row_stride, dk_head_stride;
-  int64_t dv_batch_stride, dv_row_stride, dv_head_stride;
-  const int2* work_list;  // packed problems: (key sequence, key block) per blockIdx.x
-  int* status;
-  long long* trace;  // optional cycle counters, null = off
-};
 
 template <int D>
 struct BwdConfig {
@@ -58,21 +39,6 @@ struct BwdConfig {
   static constexpr int kThreads = 512;  // 2 compute warpgroups, 1 dQ-drain warpgroup, 1 warpgroup with the MMA and load warps
   static constexpr int kTmemS = 0, kTmemDp = 128, kTmemDv = 256, kTmemDk = 256 + D;
 };
-
-__device__ __forceinline__ void cp_async_4(uint32_t smem_dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
-__device__ __forceinline__ float4 ld_shared_f4(uint32_t addr) {
-  float4 v;
-  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
-  return v;
-}
 
 template <int D>
 __global__ void __launch_bounds__(BwdConfig<D>::kThreads, 1)
@@ -560,12 +526,19 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(
   int batch_coord;
   int64_t tensor_row;
   if (!locate_row(map, row, &batch_coord, &tensor_row)) return;
-  constexpr int kPerLane = D / 32;  // 2 or 4 BF16 values
+  constexpr int kPerLane = D / 32;  // 2, 4 or 8 BF16 values
   const __nv_bfloat16* o_ptr = o + batch_coord * o_bs + tensor_row * o_rs + (int64_t)head * o_hs + lane * kPerLane;
   const __nv_bfloat16* do_ptr = dout + batch_coord * do_bs + tensor_row * do_rs + (int64_t)head * do_hs + lane * kPerLane;
   float sum = 0.f;
   if (lane * kPerLane >= map.head_dim) {
     // padding columns of a head_dim below the compiled one
+  } else if constexpr (kPerLane == 8) {
+    const uint4 a = *reinterpret_cast<const uint4*>(o_ptr), b = *reinterpret_cast<const uint4*>(do_ptr);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      sum += __uint_as_float(aw[i] << 16) * __uint_as_float(bw[i] << 16) +
+             __uint_as_float(aw[i] & 0xffff0000u) * __uint_as_float(bw[i] & 0xffff0000u);
   } else if constexpr (kPerLane == 4) {
     const uint2 a = *reinterpret_cast<const uint2*>(o_ptr), b = *reinterpret_cast<const uint2*>(do_ptr);
     sum = __uint_as_float(a.x << 16) * __uint_as_float(b.x << 16) +
@@ -586,7 +559,10 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(
     dpsum[stat] = -sum;
   }
   float* acc = dq_accum + stat * D + lane * kPerLane;
-  if constexpr (kPerLane == 4) {
+  if constexpr (kPerLane == 8) {
+    *reinterpret_cast<float4*>(acc) = make_float4(0.f, 0.f, 0.f, 0.f);
+    *reinterpret_cast<float4*>(acc + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+  } else if constexpr (kPerLane == 4) {
     *reinterpret_cast<float4*>(acc) = make_float4(0.f, 0.f, 0.f, 0.f);
   } else {
     *reinterpret_cast<float2*>(acc) = make_float2(0.f, 0.f);
@@ -609,7 +585,15 @@ __global__ void __launch_bounds__(256) bwd_postprocess_kernel(const float* __res
   const float* acc = dq_accum + ((int64_t)head * map.rows + row) * D + lane * kPerLane;
   __nv_bfloat16* out = dq + batch_coord * dq_bs + tensor_row * dq_rs + (int64_t)head * dq_hs + lane * kPerLane;
   if (lane * kPerLane >= map.head_dim) return;
-  if constexpr (kPerLane == 4) {
+  if constexpr (kPerLane == 8) {
+    const float4 v = *reinterpret_cast<const float4*>(acc), w = *reinterpret_cast<const float4*>(acc + 4);
+    uint4 packed;
+    packed.x = pack_bf16x2(v.x * scale, v.y * scale);
+    packed.y = pack_bf16x2(v.z * scale, v.w * scale);
+    packed.z = pack_bf16x2(w.x * scale, w.y * scale);
+    packed.w = pack_bf16x2(w.z * scale, w.w * scale);
+    *reinterpret_cast<uint4*>(out) = packed;
+  } else if constexpr (kPerLane == 4) {
     const float4 v = *reinterpret_cast<const float4*>(acc);
     uint2 packed;
     packed.x = pack_bf16x2(v.x * scale, v.y * scale);
@@ -646,7 +630,7 @@ static BwdWorkspace plan_workspace(const b200fa_problem& p) {
   w.lse_log2 = 0;
   w.dpsum = stat_bytes;
   w.dq_accum = 2 * stat_bytes;
-  const int compiled_dim = p.head_dim <= 64 ? 64 : 128;  // the accumulator has the compiled width
+  const int compiled_dim = p.head_dim <= 64 ? 64 : p.head_dim <= 128 ? 128 : 256;  // the accumulator has the compiled width
   const size_t acc_bytes = ((size_t)p.heads_q * w.rows * compiled_dim * 4 + 255) & ~size_t(255);
   w.work_list = w.dq_accum + acc_bytes;
   w.entries = packed ? work_list_entries(p.seqlen_k, p.batch, kBlockN) : 0;
@@ -707,7 +691,6 @@ static int launch_main(const b200fa_bwd_args& a, const BwdParams& p, dim3 grid, 
 
 template <int D>
 static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
-  using Cfg = BwdConfig<D>;
   const b200fa_problem& bp = a.problem;
   const bool packed = bp.cu_seqlens_q != nullptr;
   const BwdWorkspace w = plan_workspace(bp);
@@ -755,6 +738,7 @@ static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
   if (!p.status) return B200FA_ERR_CUDA;
   p.trace = trace_buffer();
 
+  constexpr unsigned kHeadSplit = D == 256 ? 2 : 1;  // the 256-column kernel runs one CTA per half of the head dimension
   dim3 grid;
   bool run_main = !no_keys;
   if (packed) {
@@ -766,13 +750,18 @@ static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
                                   reinterpret_cast<int32_t*>(ws + w.work_list), stream);
     if (status != B200FA_OK) return status;
     p.work_list = reinterpret_cast<const int2*>(ws + w.work_list);
-    grid = dim3((unsigned)w.entries, (unsigned)bp.heads_kv, 1);
+    grid = dim3((unsigned)w.entries, (unsigned)bp.heads_kv * kHeadSplit, 1);
   } else if (run_main) {
-    grid = dim3((unsigned)ceil_div(bp.seqlen_k, kBlockN), (unsigned)bp.heads_kv, (unsigned)bp.batch);
+    grid = dim3((unsigned)ceil_div(bp.seqlen_k, kBlockN), (unsigned)bp.heads_kv * kHeadSplit, (unsigned)bp.batch);
   }
   mark(1, stream);
   if (run_main) {
-    int status = launch_main<D>(a, p, grid, dq_accum, w.rows, stream);
+    int status;
+    if constexpr (D == 256) {
+      status = launch_bwd_main_d256(a, p, grid, dq_accum, w.rows, stream);
+    } else {
+      status = launch_main<D>(a, p, grid, dq_accum, w.rows, stream);
+    }
     if (status != B200FA_OK) return status;
   }
   mark(2, stream);
@@ -796,8 +785,10 @@ int launch_bwd(const b200fa_bwd_args& a, cudaStream_t stream) {
     case 96:
     case 128:
       return launch_bwd_d<128>(a, stream);
+    case 256:
+      return launch_bwd_d<256>(a, stream);
     default:
-      set_error("head_dim %d is not supported by the backward kernels (supported: 64, 72, 96, 128)", a.problem.head_dim);
+      set_error("head_dim %d is not supported by the backward kernels (supported: 64, 72, 96, 128, 256)", a.problem.head_dim);
       return B200FA_ERR_UNSUPPORTED;
   }
 }

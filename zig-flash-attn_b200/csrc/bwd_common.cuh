@@ -1,0 +1,47 @@
+// Shared pieces of the backward kernels: the parameter block, small shared-memory helpers and the launcher of the
+// head_dim 256 main kernel (defined in bwd_d256.cu, called from bwd.cu).
+#pragma once
+
+#include "common.h"
+#include "ptx.cuh"
+
+namespace b200fa {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct BwdParams {
+  Problem prob;
+  float scale, scale_log2;
+  const float* lse_log2;  // (heads_q, rows) : -lse * log2(e)
+  const float* dpsum;     // (heads_q, rows) : -sum_d O * dO
+  int64_t rows;           // rows of the statistics / dQ accumulator per head (batch * seqlen_q or total_q)
+  int head_dim;           // columns of the tensors (<= the compiled D; TMA zero-fills the columns in between)
+  __nv_bfloat16* dk;
+  __nv_bfloat16* dv;
+  int64_t dk_batch_stride, dk_row_stride, dk_head_stride;
+  int64_t dv_batch_stride, dv_row_stride, dv_head_stride;
+  const int2* work_list;  // packed problems: (key sequence, key block) per blockIdx.x
+  int* status;
+  long long* trace;  // optional cycle counters, null = off
+};
+
+__device__ __forceinline__ void cp_async_4(uint32_t smem_dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ float4 ld_shared_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+
+// Main kernel for head_dim in (128, 256]: grid.y = 2 * heads_kv (kv head, half of the head dimension).
+int launch_bwd_main_d256(const b200fa_bwd_args& a, const BwdParams& p, dim3 grid, float* dq_accum, int64_t stat_rows,
+                         cudaStream_t stream);
+
+}  // namespace b200fa
