@@ -33,7 +33,8 @@ def test_version_and_head_dims():
     assert library.b200fa_supports_head_dim(80, 0) == 0
     assert library.b200fa_supports_head_dim(96, 1) == 1 and library.b200fa_supports_head_dim(72, 0) == 1
     assert library.b200fa_supports_head_dim(256, 0) == 1 and library.b200fa_supports_head_dim(256, 1) == 1
-    assert library.b200fa_supports_head_dim(512, 0) == 0
+    assert library.b200fa_supports_head_dim(512, 0) == 1 and library.b200fa_supports_head_dim(512, 1) == 0
+    assert library.b200fa_supports_head_dim(384, 0) == 0
 
 
 def problem(**fields):

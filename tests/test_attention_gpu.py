@@ -317,7 +317,37 @@ def test_head_dim_256_varlen():
         mask = oracle.packed_mask(cu_q.tolist(), cu_k.tolist(), (window[0], 0) if causal else window)
         parity.check_masked((out.detach(), lse, grads), q.detach(), k.detach(), v.detach(), dout, mask,
                             notes=f"[d256 varlen {window} {causal}]")
-    # no kernel is compiled for head_dim 512
-    leaf = randn(1, 128, 2, 512)
+    # no kernel is compiled for head_dim 384
+    leaf = randn(1, 128, 2, 384)
     with pytest.raises(ValueError, match="head_dim"):
         zigfa.flash_attn_func(leaf, leaf, leaf, causal=True)
+
+
+# ------------------------------------------------------------------------------------------------ head_dim 512 (forward)
+@pytest.mark.parametrize("kind", WINDOW_KINDS)
+def test_head_dim_512_forward_matches_oracle(kind):
+    for (seqlen_q, seqlen_k), heads_name in itertools.product(SEQLENS, HEAD_LAYOUTS):
+        heads_q, heads_kv = HEAD_LAYOUTS[heads_name]
+        window, causal = window_of(kind, seqlen_k)
+        torch.manual_seed(seqlen_q * 31 + seqlen_k)
+        batch = 2 if seqlen_q <= 1024 else 1
+        q, k, v = randn(batch, seqlen_q, heads_q, 512), randn(batch, seqlen_k, heads_kv, 512), randn(batch, seqlen_k, heads_kv, 512)
+        out, lse = zigfa.flash_attn_func(q, k, v, causal=causal, window_size=window, return_attn_probs=True)
+        parity.check_fixed((out, lse, None), q, k, v, None, causal, window, notes=f"[d512 {kind} {seqlen_q}x{seqlen_k} {heads_name}]")
+
+
+def test_head_dim_512_varlen_forward_and_backward_refusal():
+    lengths_q, lengths_k = [100, 0, 300, 77, 513], [120, 40, 300, 0, 700]
+    q = randn(sum(lengths_q) + 5, 6, 512)
+    k, v = randn(sum(lengths_k) + 5, 2, 512), randn(sum(lengths_k) + 5, 2, 512)
+    cu_q, cu_k = cu_seqlens(lengths_q), cu_seqlens(lengths_k)
+    for window, causal in (((-1, -1), False), ((-1, 0), True), ((60, 10), False)):
+        out, lse = zigfa.flash_attn_varlen_func(q, k, v, cu_q, cu_k, 513, 700, causal=causal, window_size=window,
+                                                return_attn_probs=True)
+        mask = oracle.packed_mask(cu_q.tolist(), cu_k.tolist(), (window[0], 0) if causal else window)
+        parity.check_masked((out, lse, None), q, k, v, None, mask, notes=f"[d512 varlen {window} {causal}]")
+    # the backward kernels stop at head_dim 256
+    leaf = randn(1, 128, 2, 512).requires_grad_()
+    out = zigfa.flash_attn_func(leaf, leaf.detach(), leaf.detach(), causal=True)
+    with pytest.raises(ValueError, match="head_dim"):
+        out.sum().backward()

@@ -183,6 +183,31 @@ def test_config3_inter_sequence_shared_prefix(prefix):
         check_slice("dv", dv[rows, one], ref[4], None)
 
 
+def test_config3_head_dim_512_forward():
+    # the forward-only head_dim of the shared-prefix configuration
+    lengths, visible = shared_prefix_layout(8, 2048, 7, 512)
+    heads_q, heads_kv, d = 32, 8, 512
+    total = sum(lengths)
+    torch.manual_seed(3)
+    q, k, v = randn(total, heads_q, d), randn(total, heads_kv, d), randn(total, heads_kv, d)
+    cu = torch.tensor([0, *itertools.accumulate(lengths)], dtype=torch.int32, device="cuda")
+    bits = torch.from_numpy(oracle.visibility_bits_of(visible.numpy())).cuda()
+    out, lse = zigfa.flash_attn_inter_sequence_func(q, k, v, cu, cu, max(lengths), max(lengths), bits, causal=True,
+                                                    return_attn_probs=True)
+    assert torch.isfinite(out).all() and torch.isfinite(lse).all()
+    group_heads = heads_q // heads_kv
+    for g, kv_head in [(0, 0), (7, 5)]:
+        first = g * 8
+        rows = slice(int(cu[first]), int(cu[first + 8]))
+        sub_cu = [0, *itertools.accumulate(lengths[first : first + 8])]
+        mask = oracle.inter_sequence_mask(sub_cu, sub_cu, visible[first : first + 8, first : first + 8], [(-1, 0)] * 8).cuda()
+        heads = slice(kv_head * group_heads, (kv_head + 1) * group_heads)
+        one = slice(kv_head, kv_head + 1)
+        ref_out, ref_lse = oracle.masked_attention(q[rows, heads], k[rows, one], v[rows, one], mask, d**-0.5)
+        check_slice("out", out[rows, heads], ref_out, None)
+        parity.assert_lse(lse[heads, rows], ref_lse)
+
+
 def test_config4_long_context_window_shard():
     # one shard of the 8-GPU split: 2 of the 16 batch entries
     batch, seqlen, heads_q, heads_kv, d, window = 2, 32768, 32, 4, 128, (4096, 0)

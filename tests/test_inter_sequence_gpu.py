@@ -130,6 +130,14 @@ def test_layouts_match_oracle(head_dim, name):
         check_layout(build_layout(name, seed), *HEAD_LAYOUTS[heads_name], head_dim)
 
 
+@pytest.mark.parametrize("name", LAYOUTS)
+def test_layouts_forward_head_dim_512(name):
+    # head_dim 512 has a forward kernel only
+    for heads_name in HEAD_LAYOUTS:
+        torch.manual_seed(1)
+        check_layout(build_layout(name, 1), *HEAD_LAYOUTS[heads_name], 512, backward=False)
+
+
 @pytest.mark.parametrize("options", [dict(causal=True), dict(window_size=(6, 2)), dict(window_size=(-1, -1))])
 def test_scalar_windows(options):
     torch.manual_seed(3)

@@ -137,8 +137,8 @@ const char* b200fa_last_error(void) { return g_error; }
 int b200fa_version(void) { return 100; }
 
 int b200fa_supports_head_dim(int32_t head_dim, int32_t direction) {
-  (void)direction;  // every compiled head dimension has both a forward and a backward kernel
-  return head_dim == 64 || head_dim == 72 || head_dim == 96 || head_dim == 128 || head_dim == 256;
+  if (head_dim == 64 || head_dim == 72 || head_dim == 96 || head_dim == 128 || head_dim == 256) return 1;
+  return head_dim == 512 && direction == 0;  // head_dim 512: forward only
 }
 
 int b200fa_device_status(void) {

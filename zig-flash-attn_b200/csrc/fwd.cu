@@ -521,8 +521,10 @@ int launch_fwd(const b200fa_fwd_args& a, cudaStream_t stream) {
       return launch_fwd_d<128>(a, stream);
     case 256:
       return launch_fwd_256(a, stream);
+    case 512:
+      return launch_fwd_512(a, stream);
     default:
-      set_error("head_dim %d is not supported by the forward kernel (supported: 64, 72, 96, 128, 256)", a.problem.head_dim);
+      set_error("head_dim %d is not supported by the forward kernel (supported: 64, 72, 96, 128, 256, 512)", a.problem.head_dim);
       return B200FA_ERR_UNSUPPORTED;
   }
 }

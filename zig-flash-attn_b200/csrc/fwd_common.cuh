@@ -62,5 +62,6 @@ __device__ __forceinline__ FwdTile decode_tile(const FwdParams& p, int tile, int
 int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim, int tile_rows, int kv_box_rows,
                     FwdParams* p, CUtensorMap* map_q, CUtensorMap* map_k, CUtensorMap* map_v, bool* nothing_to_do);
 int launch_fwd_256(const b200fa_fwd_args& a, cudaStream_t stream);
+int launch_fwd_512(const b200fa_fwd_args& a, cudaStream_t stream);
 
 }  // namespace b200fa

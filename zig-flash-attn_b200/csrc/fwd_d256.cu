@@ -10,21 +10,30 @@
 // runs the PV product of block n and the scores of block n + 2. Per block the tensor work (2 x 512 cycles) about equals
 // the softmax work of one warpgroup, which is why one softmax warpgroup is enough here.
 // Warps 0-3: softmax and epilogue (thread = query row), warp 4: MMA issue, warp 5: TMA loads, warps 6-7: spare.
+//
+// head_dim 512 (kSplit = 2) runs the same kernel: an accumulator of 512 columns would take all of TMEM, so a work
+// item is split in two, one per 256 output columns (tile index = 2 * item + half). Both halves compute the full
+// scores (reduction over 512 columns: a key block is two ring slots) and their own half of P V. The query tile takes
+// 128 KB of shared memory, which leaves three ring slots.
 #include "fwd_common.cuh"
 
 namespace b200fa {
 
 namespace d256 {
-constexpr int D = 256;
+constexpr int D = 256;                            // output columns of a CTA; the reduction runs over kSplit * D columns
 constexpr int kSubN = 64;                         // keys per block
-constexpr int kStages = 5;                        // K/V ring slots of 64 x 256 BF16
-constexpr int kQBytes = kBlockM * D * 2;          // 64 KB
-constexpr int kKvBytes = kSubN * D * 2;           // 32 KB
+constexpr int kKvBytes = kSubN * D * 2;           // 32 KB: one ring slot (64 keys x 256 columns)
 constexpr int kQPanel = kBlockM * 128;            // 64-column panel of Q
 constexpr int kKvPanel = kSubN * 128;             // 64-column panel of K / V
-constexpr int kSmemBytes = kQBytes + kStages * kKvBytes + 1024 + 256;
 constexpr int kThreads = 256;
 constexpr int kTmemO = 256;
+template <int kSplit>
+struct Config {
+  static constexpr int kStages = kSplit == 1 ? 5 : 3;            // K/V ring slots
+  static constexpr int kQBytes = kBlockM * D * kSplit * 2;       // 64 KB or 128 KB
+  static constexpr int kSmemBytes = kQBytes + kStages * kKvBytes + 1024 + 256;
+  static_assert(kSmemBytes <= 232448, "shared memory exceeds the per-CTA limit");
+};
 }  // namespace d256
 
 // Yields the key blocks of a KeyCursor as 64-key halves.
@@ -49,11 +58,14 @@ struct SubBlockCursor {
   }
 };
 
+template <int kSplit>
 __global__ void __launch_bounds__(d256::kThreads, 1)
 fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ FwdParams p) {
   using namespace d256;
-  constexpr int NS = kStages;
+  constexpr int NS = Config<kSplit>::kStages;
+  constexpr int kQBytes = Config<kSplit>::kQBytes;
+  const int num_tiles = p.num_tiles * kSplit;  // tile = kSplit * work item + half of the output columns
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t smem_q = smem_base;
@@ -111,18 +123,26 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     if (lane == 0) {
       uint32_t ring = 0, q_count = 0;
       bool ok = true;
-      auto load_kv = [&](const CUtensorMap* map, int head, int row, int batch_coord) -> bool {
+      // One ring slot: 64 rows x 256 columns starting at column col0.
+      auto load_slot = [&](const CUtensorMap* map, int col0, int head, int row, int batch_coord) -> bool {
         const uint32_t slot = ring % NS, phase = (ring / NS) & 1;
         if (!mbar_wait(bar_kv_empty + 8 * slot, phase ^ 1, wctx, kWaitKvEmpty)) return false;
         const uint32_t bar = bar_kv_full + 8 * slot;
         mbar_expect_tx(bar, kKvBytes);
 #pragma unroll
-        for (int h = 0; h < 4; ++h) tma_load_4d(smem_kv + slot * kKvBytes + h * kKvPanel, map, bar, h * 64, head, row, batch_coord);
+        for (int h = 0; h < 4; ++h)
+          tma_load_4d(smem_kv + slot * kKvBytes + h * kKvPanel, map, bar, col0 + h * 64, head, row, batch_coord);
         ++ring;
         return true;
       };
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-        FwdTile t = decode_tile(p, tile, kBlockM);
+      auto load_k = [&](int head, int row, int batch_coord) -> bool {  // all reduction columns: kSplit slots
+        for (int part = 0; part < kSplit; ++part)
+          if (!load_slot(&map_k, part * D, head, row, batch_coord)) return false;
+        return true;
+      };
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        FwdTile t = decode_tile(p, tile / kSplit, kBlockM);
+        const int dh = tile % kSplit;
         if (!t.valid) continue;
         const int n_blocks = count_blocks(t);
         if (n_blocks == 0) continue;
@@ -134,17 +154,18 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         ++q_count;
         mbar_expect_tx(bar_q_full, kQBytes);
 #pragma unroll
-        for (int h = 0; h < 4; ++h) tma_load_4d(smem_q + h * kQPanel, &map_q, bar_q_full, h * 64, t.head, t.s.q0 + t.m0, t.s.batch_coord);
+        for (int h = 0; h < 4 * kSplit; ++h)
+          tma_load_4d(smem_q + h * kQPanel, &map_q, bar_q_full, h * 64, t.head, t.s.q0 + t.m0, t.s.batch_coord);
         for (int i = 0; ok && i < imin(2, n_blocks); ++i) {
           cur_k.next(&kb);
-          ok = load_kv(&map_k, t.kv_head, kb.row, t.s.batch_coord);
+          ok = load_k(t.kv_head, kb.row, t.s.batch_coord);
         }
         for (int n = 0; ok && n < n_blocks; ++n) {
           cur_v.next(&kb);
-          ok = load_kv(&map_v, t.kv_head, kb.row, t.s.batch_coord);
+          ok = load_slot(&map_v, dh * D, t.kv_head, kb.row, t.s.batch_coord);
           if (ok && n + 2 < n_blocks) {
             cur_k.next(&kb);
-            ok = load_kv(&map_k, t.kv_head, kb.row, t.s.batch_coord);
+            ok = load_k(t.kv_head, kb.row, t.s.batch_coord);
           }
         }
       }
@@ -157,18 +178,30 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       uint32_t ring = 0, q_count = 0, blocks = 0;  // blocks: PV products issued so far (all work items)
       uint32_t p_phase[2] = {0, 0};
       bool ok = true;
-      auto issue_s = [&](int buffer, uint32_t k_smem) {
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          umma_ss(tmem_base + buffer * 128, umma_smem_desc(smem_q + (kk >> 2) * kQPanel + (kk & 3) * 32, 16, 1024),
-                  umma_smem_desc(k_smem + (kk >> 2) * kKvPanel + (kk & 3) * 32, 16, 1024), idesc_s, kk > 0);
-        }
-      };
       auto wait_kv = [&](uint32_t index) -> bool {
         return mbar_wait(bar_kv_full + 8 * (index % NS), (index / NS) & 1, wctx, kWaitKvFull);
       };
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-        FwdTile t = decode_tile(p, tile, kBlockM);
+      // S = Q K^T over the kSplit ring slots of a key block; each slot is released as soon as its MMAs are issued.
+      auto issue_s = [&](int buffer) -> bool {
+        for (int part = 0; part < kSplit; ++part) {
+          const uint32_t k_index = ring++;
+          if (!wait_kv(k_index)) return false;
+          tc_fence_after();
+          const uint32_t k_smem = smem_kv + (k_index % NS) * kKvBytes;
+          const uint32_t q_smem = smem_q + part * 4 * kQPanel;
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            umma_ss(tmem_base + buffer * 128, umma_smem_desc(q_smem + (kk >> 2) * kQPanel + (kk & 3) * 32, 16, 1024),
+                    umma_smem_desc(k_smem + (kk >> 2) * kKvPanel + (kk & 3) * 32, 16, 1024), idesc_s, part > 0 || kk > 0);
+          }
+          tc_commit(bar_kv_empty + 8 * (k_index % NS));
+        }
+        tc_commit(bar_s_full + 8 * buffer);
+        return true;
+      };
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        FwdTile t = decode_tile(p, tile / kSplit, kBlockM);
+        const int dh = tile % kSplit;
         if (!t.valid) continue;
         const int n_blocks = count_blocks(t);
         if (n_blocks == 0) continue;
@@ -176,14 +209,7 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         ++q_count;
         if (!mbar_wait(bar_q_full, q_phase, wctx, kWaitQFull)) { ok = false; break; }
         // The S buffers alternate with the block index of the work item; their barrier phases count per buffer.
-        for (int i = 0; ok && i < imin(2, n_blocks); ++i) {
-          const uint32_t k_index = ring++;
-          if (!wait_kv(k_index)) { ok = false; break; }
-          tc_fence_after();
-          issue_s(i, smem_kv + (k_index % NS) * kKvBytes);
-          tc_commit(bar_s_full + 8 * i);
-          tc_commit(bar_kv_empty + 8 * (k_index % NS));
-        }
+        for (int i = 0; ok && i < imin(2, n_blocks); ++i) ok = issue_s(i);
         for (int n = 0; ok && n < n_blocks; ++n) {
           const int buffer = n & 1;
           const uint32_t v_index = ring++;
@@ -201,14 +227,7 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           tc_commit(bar_pv_done);
           tc_commit(bar_kv_empty + 8 * (v_index % NS));
           ++blocks;
-          if (n + 2 < n_blocks) {
-            const uint32_t k_index = ring++;
-            if (!wait_kv(k_index)) { ok = false; break; }
-            tc_fence_after();
-            issue_s(buffer, smem_kv + (k_index % NS) * kKvBytes);
-            tc_commit(bar_s_full + 8 * buffer);
-            tc_commit(bar_kv_empty + 8 * (k_index % NS));
-          }
+          if (n + 2 < n_blocks) ok = issue_s(buffer);
         }
         if (ok) tc_commit(bar_q_empty);
       }
@@ -223,8 +242,9 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     uint32_t blocks = 0;
     uint32_t s_phase[2] = {0, 0};
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-      FwdTile t = decode_tile(p, tile, kBlockM);
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      FwdTile t = decode_tile(p, tile / kSplit, kBlockM);
+      const int dh = tile % kSplit;
       if (!t.valid) continue;
       const int row = t.m0 + row_in_tile;
       SubBlockCursor cur;
@@ -309,6 +329,10 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           tmem_st16(t_s + 64 + 16 * c, packed);
         }
         l += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
+        // Observe the PV product of the previous block before releasing this one. The scores of block n only prove
+        // that PV(n - 2) has completed, so without this wait the barrier could be two completions away from the one
+        // the epilogue waits for, which a parity wait cannot tell apart from "done".
+        if (tile_blocks > 0 && !mbar_wait_warp(bar_pv_done, (blocks - 1) & 1, wctx, kWaitPvDone)) { ok = false; break; }
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar_p_full + 8 * buffer);
@@ -319,14 +343,14 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // ---- epilogue
       const bool row_valid = row < t.s.lq;
       __nv_bfloat16* o_row = p.o + t.s.batch_coord * p.o_batch_stride + (int64_t)(t.s.q0 + row) * p.o_row_stride +
-                             (int64_t)t.head * p.o_head_stride;
+                             (int64_t)t.head * p.o_head_stride + dh * D;
       float* lse_ptr = p.lse + t.s.batch_coord * p.lse_batch_stride + (int64_t)t.head * p.lse_head_stride + t.s.q0 + row;
       if (tile_blocks == 0) {
         if (row_valid) {
           const uint4 zero = make_uint4(0, 0, 0, 0);
 #pragma unroll
           for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(o_row)[c] = zero;
-          *lse_ptr = -INFINITY;
+          if (dh == 0) *lse_ptr = -INFINITY;
         }
         continue;
       }
@@ -350,7 +374,7 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
         }
       }
-      if (row_valid) {
+      if (row_valid && dh == 0) {  // both halves hold the same statistics
         const float mc = (m == -INFINITY) ? 0.f : m * scale_log2;
         *lse_ptr = l > 0.f ? (mc + log2f(l)) * 0.69314718055994531f : -INFINITY;
       }
@@ -368,24 +392,30 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (warp == 4) tmem_dealloc(tmem_base, 512);
 }
 
-int launch_fwd_256(const b200fa_fwd_args& a, cudaStream_t stream) {
+template <int kSplit>
+static int launch_fwd_wide(const b200fa_fwd_args& a, cudaStream_t stream) {
+  using Cfg = d256::Config<kSplit>;
   FwdParams p;
   CUtensorMap map_q, map_k, map_v;
   bool nothing_to_do = false;
-  int status = prepare_forward(a, stream, d256::D, kBlockM, d256::kSubN, &p, &map_q, &map_k, &map_v, &nothing_to_do);
+  int status = prepare_forward(a, stream, d256::D * kSplit, kBlockM, d256::kSubN, &p, &map_q, &map_k, &map_v, &nothing_to_do);
   if (status != B200FA_OK || nothing_to_do) return status;
   static bool attribute_set = false;
   if (!attribute_set) {
-    B200FA_CUDA_CHECK(cudaFuncSetAttribute(fwd_d256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, d256::kSmemBytes));
+    B200FA_CUDA_CHECK(cudaFuncSetAttribute(fwd_d256_kernel<kSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     attribute_set = true;
   }
   int sms = 0;
   status = device_sm_count(&sms);
   if (status != B200FA_OK) return status;
-  const int grid = p.num_tiles < sms ? p.num_tiles : sms;
-  fwd_d256_kernel<<<grid, d256::kThreads, d256::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+  const int tiles = p.num_tiles * kSplit;
+  const int grid = tiles < sms ? tiles : sms;
+  fwd_d256_kernel<kSplit><<<grid, d256::kThreads, Cfg::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
   B200FA_CUDA_CHECK(cudaGetLastError());
   return B200FA_OK;
 }
+
+int launch_fwd_256(const b200fa_fwd_args& a, cudaStream_t stream) { return launch_fwd_wide<1>(a, stream); }
+int launch_fwd_512(const b200fa_fwd_args& a, cudaStream_t stream) { return launch_fwd_wide<2>(a, stream); }
 
 }  // namespace b200fa
