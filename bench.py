@@ -1,6 +1,6 @@
 """Benchmark of the attention hot path on N GPUs of one node.
 
-    python bench.py --gpus N --steps K --warmup W [--workload c1|c4] [--impl reference]
+    python bench.py --gpus N --steps K --warmup W [--workload c1|c1s|d256s|c4] [--impl reference]
 
 One step = one forward + one backward pass of the workload on every rank. Default workload "c1" is the configuration
 the headline metric is quoted on: fixed-length causal GQA, batch 4, seqlen 8192, 32 query / 8 key heads, head_dim
@@ -33,6 +33,8 @@ WORKLOADS = {
                name="fixed-length causal GQA fwd+bwd: batch 4, seqlen 8192, heads 32/8, head_dim 128"),
     "c1s": dict(batch=1, seqlen=8192, heads_q=32, heads_kv=8, head_dim=128, window=(-1, 0), seed=1,
                 name="one batch entry of c1 (profiling case): batch 1, seqlen 8192, heads 32/8, head_dim 128, causal"),
+    "d256s": dict(batch=1, seqlen=8192, heads_q=16, heads_kv=4, head_dim=256, window=(-1, 0), seed=3,
+                  name="head_dim 256 profiling case: batch 1, seqlen 8192, heads 16/4, head_dim 256, causal"),
     "c4": dict(batch=16, seqlen=32768, heads_q=32, heads_kv=4, head_dim=128, window=(4096, 0), seed=4,
                name="long-context sharded fwd+bwd: batch 16, seqlen 32768, heads 32/4, head_dim 128, window (4096, 0)"),
 }
@@ -356,14 +358,15 @@ def main():
             "e2e": {"value": total_flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "pipeline": "copies of neighbouring steps overlap the kernels (3 streams, 2 device buffer sets)"},
-            "roofline": {"kernel": "bwd_kernel<128> (dK/dV/dQ main)", "bound": "tensor",
+            "roofline": {"kernel": ("bwd_d256_kernel" if d > 128 else f"bwd_kernel<{64 if d <= 64 else 128}>") + " (dK/dV/dQ main)",
+                         "bound": "tensor",
                          "achieved": flops_bwd / (ms_main * 1e-3) / 1e12, "peak": peaks["burst"], "unit": "TFLOP/s",
                          "frac": flops_bwd / (ms_main * 1e-3) / 1e12 / peaks["burst"],
                          # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture on one batch entry of this
                          # workload (profiles/bwd_kernel_d128_c1s.md: 429.7 MB), scaled by the batch entries per launch
                          "traffic": 429.7e6 * batch if options.workload in ("c1", "c1s") else None,
                          "peak_source": f"{peaks['source']} cuBLAS BF16 burst", "sustained_peak": peaks["sustained"]},
-            "roofline_fwd": {"kernel": "fwd_kernel<128>", "bound": "tensor", "achieved": flops_fwd / (ms_fwd * 1e-3) / 1e12,
+            "roofline_fwd": {"kernel": "fwd_d256_kernel" if d > 128 else f"fwd_kernel<{64 if d <= 64 else 128}>", "bound": "tensor", "achieved": flops_fwd / (ms_fwd * 1e-3) / 1e12,
                              "peak": peaks["burst"], "unit": "TFLOP/s",
                              "frac": flops_fwd / (ms_fwd * 1e-3) / 1e12 / peaks["burst"]},
             "clocks": clocks, "device_status": status,
