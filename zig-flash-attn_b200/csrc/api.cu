@@ -85,6 +85,15 @@ int device_sm_count(int* count) {
   return B200FA_OK;
 }
 
+int set_dynamic_smem_once(const void* kernel, int bytes, bool (&done)[64]) {
+  int device = 0;
+  B200FA_CUDA_CHECK(cudaGetDevice(&device));
+  if (device >= 0 && device < 64 && done[device]) return B200FA_OK;
+  B200FA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  if (device >= 0 && device < 64) done[device] = true;
+  return B200FA_OK;
+}
+
 int* device_status_word() {
   static int* cached[64] = {nullptr};
   int device = 0;

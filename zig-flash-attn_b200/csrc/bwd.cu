@@ -678,11 +678,9 @@ static int launch_main(const b200fa_bwd_args& a, const BwdParams& p, dim3 grid, 
     if (status != B200FA_OK) return status;
   }
 
-  static bool attribute_set = false;
-  if (!attribute_set) {
-    B200FA_CUDA_CHECK(cudaFuncSetAttribute(bwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    attribute_set = true;
-  }
+  static bool attribute_set[64] = {false};
+  status = set_dynamic_smem_once(reinterpret_cast<const void*>(&bwd_kernel<D>), Cfg::kSmemBytes, attribute_set);
+  if (status != B200FA_OK) return status;
   bwd_kernel<D><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_q, map_k, map_v, map_do, map_dq, p);
   B200FA_CUDA_CHECK(cudaGetLastError());
 

@@ -505,11 +505,9 @@ int launch_bwd_main_d256(const b200fa_bwd_args& a, const BwdParams& p, dim3 grid
                                stat_rows * D, D, (int64_t)bp.heads_q * stat_rows * D, 128, kStageRows);
     if (status != B200FA_OK) return status;
   }
-  static bool attribute_set = false;
-  if (!attribute_set) {
-    B200FA_CUDA_CHECK(cudaFuncSetAttribute(bwd_d256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    attribute_set = true;
-  }
+  static bool attribute_set[64] = {false};
+  status = set_dynamic_smem_once(reinterpret_cast<const void*>(&bwd_d256_kernel), kSmemBytes, attribute_set);
+  if (status != B200FA_OK) return status;
   bwd_d256_kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, map_do, map_dq, p);
   B200FA_CUDA_CHECK(cudaGetLastError());
   return B200FA_OK;

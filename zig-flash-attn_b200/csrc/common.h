@@ -41,6 +41,9 @@ int encode_tensor_map(CUtensorMap* map, const void* base, CUtensorMapDataType ty
 Problem to_problem(const b200fa_problem& in);
 
 int device_sm_count(int* count);
+// Raises the dynamic shared-memory limit of `kernel` once per device (function attributes are per device; `done` is
+// the caller's per-kernel record, indexed by device ordinal).
+int set_dynamic_smem_once(const void* kernel, int bytes, bool (&done)[64]);
 
 // Device address of the library's status word on the current device (null + error text on failure).
 int* device_status_word();

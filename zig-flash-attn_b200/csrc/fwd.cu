@@ -497,11 +497,9 @@ static int launch_fwd_d(const b200fa_fwd_args& a, cudaStream_t stream) {
   bool nothing_to_do = false;
   int status = prepare_forward(a, stream, D, kFwdTileM, kBlockN, &p, &map_q, &map_k, &map_v, &nothing_to_do);
   if (status != B200FA_OK || nothing_to_do) return status;
-  static bool attribute_set = false;
-  if (!attribute_set) {
-    B200FA_CUDA_CHECK(cudaFuncSetAttribute(fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    attribute_set = true;
-  }
+  static bool attribute_set[64] = {false};
+  status = set_dynamic_smem_once(reinterpret_cast<const void*>(&fwd_kernel<D>), Cfg::kSmemBytes, attribute_set);
+  if (status != B200FA_OK) return status;
   int sms = 0;
   status = device_sm_count(&sms);
   if (status != B200FA_OK) return status;
