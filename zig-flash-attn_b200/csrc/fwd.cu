@@ -44,6 +44,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   constexpr int kPolyPeriod = 4, kPolyCount = 0;
   // Keep all 128 scores of a row in registers (true) or read the lower half from TMEM a second time (false).
   constexpr bool kSinglePass = false;
+  // The PV product of a block is issued in two halves: keys [64,128) as soon as their probabilities are stored, keys
+  // [0,64) after the rest, so the first half runs while the softmax warps still work on the second.
+#ifndef B200FA_SPLIT_PV
+#define B200FA_SPLIT_PV 1
+#endif
+  constexpr bool kSplitPv = B200FA_SPLIT_PV && !kSinglePass;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t smem_q = smem_base;
@@ -57,7 +63,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   const uint32_t bar_s_full = bar_kv_empty + 8 * NS;   // [2]
   const uint32_t bar_p_full = bar_s_full + 16;         // [2]
   const uint32_t bar_pv_done = bar_p_full + 16;        // [2]
-  const uint32_t tmem_slot = bar_pv_done + 16;         // 4 bytes
+  const uint32_t bar_p_half = bar_pv_done + 16;        // [2]
+  const uint32_t tmem_slot = bar_p_half + 16;          // 4 bytes
   const uint32_t abort_slot = tmem_slot + 4;           // 4 bytes
   volatile int* abort_flag =
       reinterpret_cast<volatile int*>(smem_raw + (abort_slot - smem_u32(smem_raw)));
@@ -80,6 +87,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_s_full + 8 * i, 1);
       mbar_init(bar_p_full + 8 * i, 128);
+      mbar_init(bar_p_half + 8 * i, 128);
       mbar_init(bar_pv_done + 8 * i, 1);
     }
     fence_barrier_init();
@@ -155,12 +163,30 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                   umma_smem_desc(k_smem + off, 16, 1024), idesc_s, kk > 0);
         }
       };
-      auto issue_pv = [&](int stage, uint32_t v_smem, bool accumulate) {
+      // O += P V over the key steps [first, first + count) of the block (16 keys per step).
+      auto issue_pv_steps = [&](int stage, uint32_t v_smem, int first, int count, bool accumulate) {
 #pragma unroll
-        for (int kk = 0; kk < kBlockN / 16; ++kk) {
+        for (int kk = first; kk < first + count; ++kk) {
           umma_ts(tmem_base + Cfg::kTmemO + stage * D, tmem_base + Cfg::kTmemS + stage * 128 + 64 + kk * 8,
-                  umma_smem_desc(v_smem + kk * 2048, Cfg::kPanelBytes, 1024), idesc_pv, accumulate || kk > 0);
+                  umma_smem_desc(v_smem + kk * 2048, Cfg::kPanelBytes, 1024), idesc_pv, accumulate || kk > first);
         }
+      };
+      // The whole product of a stage: with kSplitPv the upper key half goes first, behind its own barrier.
+      auto issue_pv = [&](int stage, uint32_t v_smem, bool accumulate, uint32_t phase) -> bool {
+        constexpr int kSteps = kBlockN / 16;
+        if (kSplitPv) {
+          if (!mbar_wait(bar_p_half + 8 * stage, phase, wctx, kWaitPFull)) return false;
+          tc_fence_after();
+          issue_pv_steps(stage, v_smem, kSteps / 2, kSteps / 2, accumulate);
+        }
+        if (!mbar_wait_traced(bar_p_full + 8 * stage, phase, wctx, kWaitPFull, 17 + stage, false)) return false;
+        tc_fence_after();
+        if (kSplitPv) {
+          issue_pv_steps(stage, v_smem, 0, kSteps / 2, true);
+        } else {
+          issue_pv_steps(stage, v_smem, 0, kSteps, accumulate);
+        }
+        return true;
       };
       auto wait_kv = [&](uint32_t index) -> bool {
         return mbar_wait_traced(bar_kv_full + 8 * (index % NS), (index / NS) & 1, wctx, kWaitKvFull, 16, false);
@@ -196,17 +222,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           const uint32_t v_smem = smem_kv + (v_index % NS) * Cfg::kTileBytes;
           const uint32_t k_smem = smem_kv + (k_index % NS) * Cfg::kTileBytes;
           const uint32_t phase = blocks & 1;
-          if (!mbar_wait_traced(bar_p_full, phase, wctx, kWaitPFull, 17, false)) { ok = false; break; }
-          tc_fence_after();
-          issue_pv(0, v_smem, !first);
+          if (!issue_pv(0, v_smem, !first, phase)) { ok = false; break; }
           tc_commit(bar_pv_done);
           if (more) {
             issue_s(0, k_smem);
             tc_commit(bar_s_full);
           }
-          if (!mbar_wait_traced(bar_p_full + 8, phase, wctx, kWaitPFull, 18, false)) { ok = false; break; }
-          tc_fence_after();
-          issue_pv(1, v_smem, !first);
+          if (!issue_pv(1, v_smem, !first, phase)) { ok = false; break; }
           tc_commit(bar_pv_done + 8);
           tc_commit(bar_kv_empty + 8 * (v_index % NS));
           if (more) {
@@ -352,6 +374,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           tmem_ld32(t_s, reinterpret_cast<uint32_t*>(low));
           tmem_ld32(t_s + 32, reinterpret_cast<uint32_t*>(low) + 32);
           exponentiate(high, 32);
+          if (kSplitPv) {  // the probabilities of keys [64,128) are in TMEM: their half of the PV product may start
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar_p_half + 8 * stage);
+          }
           tc_wait_ld();
           if (masked) apply_mask(low, 0);
           exponentiate(low, 0);
