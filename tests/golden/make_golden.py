@@ -1,7 +1,7 @@
 """Generates the golden fixtures of tests/golden/ from the reference's own oracle code.
 
-Run in the build container, where the reference checkout is mounted:
-    python tests/golden/make_golden.py /root/reference
+Run where a checkout of the reference is available (it is not needed to run the tests):
+    python tests/golden/make_golden.py <path to the reference checkout>
 It imports the reference's tests/reference.py (pure PyTorch) and stores, for seeded inputs:
   * float64 attention outputs and gradients of `stable_attention_f64` (reference tests/reference.py:192-247),
   * the masks of `visible_keys`, `varlen_visible`, `inter_sequence_visible` (reference tests/reference.py:10-19,
@@ -67,4 +67,6 @@ def main(reference_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit(__doc__)
+    main(sys.argv[1])
