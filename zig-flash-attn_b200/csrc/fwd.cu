@@ -14,6 +14,8 @@
 // Softmax runs in the log2 domain with a lazy rescale: the running reference maximum only moves when the block
 // maximum exceeds it by more than 8 (in log2 units), so O is almost never rescaled (reference
 // zig/flash_fwd_sm100.zig:963-976).
+#include <atomic>
+
 #include "fwd_common.cuh"
 
 namespace b200fa {
@@ -26,7 +28,7 @@ struct FwdConfig {
   static constexpr int kPanelBytes = kBlockM * 128;
   static constexpr int kSmemQ = 2 * kTileBytes;
   static constexpr int kSmemKv = kStages * kTileBytes;
-  static constexpr int kSmemBytes = kSmemQ + kSmemKv + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kSmemQ + kSmemKv + 1024 /*alignment slack*/ + 512 /*barriers, tile queue*/;
   static constexpr int kThreads = 384;  // 2 softmax warpgroups + 1 warpgroup holding the MMA and TMA warps
   static constexpr int kTmemS = 0;
   static constexpr int kTmemO = 256;
@@ -66,6 +68,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   const uint32_t bar_p_half = bar_pv_done + 16;        // [2]
   const uint32_t tmem_slot = bar_p_half + 16;          // 4 bytes
   const uint32_t abort_slot = tmem_slot + 4;           // 4 bytes
+  TileQueue tiles;
+  tiles.place(bar_base + 384);                         // the barriers above end below byte 256
   volatile int* abort_flag =
       reinterpret_cast<volatile int*>(smem_raw + (abort_slot - smem_u32(smem_raw)));
   volatile uint32_t* tmem_ptr_smem =
@@ -90,6 +94,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       mbar_init(bar_p_half + 8 * i, 128);
       mbar_init(bar_pv_done + 8 * i, 1);
     }
+    tiles.init(1 + 8);  // the MMA thread and the eight softmax warps
     fence_barrier_init();
   }
   if (warp == 8) {
@@ -128,7 +133,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         ++ring;
         return true;
       };
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      uint32_t drawn = 0;
+      for (int tile; ok && (tile = tiles.push(drawn, p.tile_counter, p.num_tiles, wctx)) >= 0;) {
         FwdTile t = decode_tile(p, tile);
         if (!t.valid) continue;
         KeyCursor cur;
@@ -191,7 +197,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       auto wait_kv = [&](uint32_t index) -> bool {
         return mbar_wait_traced(bar_kv_full + 8 * (index % NS), (index / NS) & 1, wctx, kWaitKvFull, 16, false);
       };
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      uint32_t popped = 0;
+      for (int tile; ok && (tile = tiles.pop_thread(popped, wctx)) >= 0;) {
         FwdTile t = decode_tile(p, tile);
         if (!t.valid) continue;
         KeyCursor cur;
@@ -261,7 +268,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     const float scale_log2 = p.scale_log2;
     uint32_t blocks = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+    uint32_t popped = 0;
+    for (int tile; ok && (tile = tiles.pop_warp(popped, wctx)) >= 0;) {
       FwdTile t = decode_tile(p, tile);
       if (!t.valid) continue;
       const int row = t.m0 + stage * kBlockM + row_in_stage;  // row within the sequence
@@ -452,6 +460,29 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 
 // -------------------------------------------------------------------------------------------------- host side
 
+// Work-item counters of the persistent kernels: a ring inside the library (the library allocates no device memory).
+// Every launch takes the next slot and zeroes it with a memset node on its own stream ahead of the kernel, so two
+// launches share a slot only if kTileCounters other launches were issued in between.
+constexpr unsigned kTileCounters = 4096;
+static __device__ int g_tile_counters[kTileCounters];
+
+int acquire_tile_counter(cudaStream_t stream, int** counter) {
+  static int* base[64] = {nullptr};
+  static std::atomic<unsigned> next{0};
+  int device = 0;
+  B200FA_CUDA_CHECK(cudaGetDevice(&device));
+  B200FA_REQUIRE(device >= 0 && device < 64, "device ordinal %d is out of range", device);
+  if (!base[device]) {
+    void* address = nullptr;
+    B200FA_CUDA_CHECK(cudaGetSymbolAddress(&address, g_tile_counters));
+    base[device] = static_cast<int*>(address);
+  }
+  int* slot = base[device] + next.fetch_add(1) % kTileCounters;
+  B200FA_CUDA_CHECK(cudaMemsetAsync(slot, 0, sizeof(int), stream));
+  *counter = slot;
+  return B200FA_OK;
+}
+
 int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim, int tile_rows, int kv_box_rows,
                     FwdParams* params, CUtensorMap* map_q, CUtensorMap* map_k, CUtensorMap* map_v, bool* nothing_to_do) {
   const b200fa_problem& bp = a.problem;
@@ -470,6 +501,7 @@ int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim,
   p.lse_batch_stride = packed ? 0 : a.lse_stride[0];
   p.lse_head_stride = a.lse_stride[1];
   p.work_list = nullptr;
+  p.tile_counter = nullptr;
   p.m_blocks = 0;
   p.head_dim = bp.head_dim;
   p.status = device_status_word();
@@ -511,6 +543,8 @@ int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim,
   status = encode_tensor_map(map_v, v_base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, no_keys ? 1 : bp.heads_kv, k_rows,
                              tensor_batch, no_keys ? D : a.v_stride[2], no_keys ? D : a.v_stride[1],
                              no_keys ? D : (packed ? k_rows * a.v_stride[1] : a.v_stride[0]), 64, kv_box_rows);
+  if (status != B200FA_OK) return status;
+  status = acquire_tile_counter(stream, &p.tile_counter);
   if (status != B200FA_OK) return status;
   *nothing_to_do = false;
   return B200FA_OK;

@@ -12,6 +12,7 @@ struct FwdParams {
   int64_t o_batch_stride, o_row_stride, o_head_stride;
   float* lse;
   int64_t lse_batch_stride, lse_head_stride;
+  int* tile_counter;      // zero at launch; the CTAs draw their work items from it (TileQueue)
   const int2* work_list;  // packed problems: (sequence, block) per entry; null for fixed length
   int m_blocks;           // fixed length: work items per (batch, head)
   int num_tiles;
@@ -24,6 +25,61 @@ struct FwdTile {
   int seq, head, kv_head, m0;
   SeqInfo s;
   bool valid;
+};
+
+// Dynamic work distribution of the persistent kernels. One producer thread (the TMA warp) draws tile indices from a
+// global counter and publishes them through a ring in shared memory; every other role pops them in the same order.
+// A CTA that finishes a light tile early simply draws the next one, so the tail of a launch is as long as one tile,
+// not as long as the imbalance of a static assignment (the reference's persistent kernels fetch tiles from an atomic
+// counter as well, zig/tile_scheduler.zig:374-430).
+struct TileQueue {
+  static constexpr int kSlots = 4;
+  static constexpr int kBytes = 4 * kSlots + 16 * kSlots;  // ring of tile indices, full and empty barriers
+  uint32_t ring, bar_full, bar_empty;
+  __device__ __forceinline__ void place(uint32_t smem) {
+    bar_full = smem;
+    bar_empty = smem + 8 * kSlots;
+    ring = smem + 16 * kSlots;
+  }
+  // One thread, before the barriers are used; `consumers` = arrivals per pop round (one per consumer warp).
+  __device__ __forceinline__ void init(int consumers) const {
+    for (int i = 0; i < kSlots; ++i) {
+      mbar_init(bar_full + 8 * i, 1);
+      mbar_init(bar_empty + 8 * i, consumers);
+    }
+  }
+  // Producer thread: the next tile of this CTA, -1 when the launch has no more tiles, -2 when a wait ran out of time.
+  __device__ __forceinline__ int push(uint32_t& n, int* counter, int num_tiles, const WaitCtx& ctx) const {
+    const uint32_t slot = n % kSlots, phase = (n / kSlots) & 1;
+    if (!mbar_wait(bar_empty + 8 * slot, phase ^ 1, ctx, kWaitTile)) return -2;
+    int tile = atomicAdd(counter, 1);
+    if (tile >= num_tiles) tile = -1;
+    asm volatile("st.shared.b32 [%0], %1;" ::"r"(ring + 4 * slot), "r"(tile) : "memory");
+    mbar_arrive(bar_full + 8 * slot);  // release: the store above is visible to whoever sees this phase complete
+    ++n;
+    return tile;
+  }
+  // Consumer, a single thread (the MMA issuer).
+  __device__ __forceinline__ int pop_thread(uint32_t& n, const WaitCtx& ctx) const {
+    const uint32_t slot = n % kSlots, phase = (n / kSlots) & 1;
+    if (!mbar_wait(bar_full + 8 * slot, phase, ctx, kWaitTile)) return -2;
+    int tile;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tile) : "r"(ring + 4 * slot) : "memory");
+    mbar_arrive(bar_empty + 8 * slot);
+    ++n;
+    return tile;
+  }
+  // Consumer, all 32 lanes of a warp together (one arrival per warp).
+  __device__ __forceinline__ int pop_warp(uint32_t& n, const WaitCtx& ctx) const {
+    const uint32_t slot = n % kSlots, phase = (n / kSlots) & 1;
+    if (!mbar_wait_warp(bar_full + 8 * slot, phase, ctx, kWaitTile)) return -2;
+    int tile;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tile) : "r"(ring + 4 * slot) : "memory");
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(bar_empty + 8 * slot);
+    ++n;
+    return tile;
+  }
 };
 
 // `tile_rows` = query rows per work item (256 for the two-stage kernel, 128 for the head_dim 256 kernel).
@@ -61,6 +117,9 @@ __device__ __forceinline__ FwdTile decode_tile(const FwdParams& p, int tile, int
 // needed. Defined in fwd.cu.
 int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim, int tile_rows, int kv_box_rows,
                     FwdParams* p, CUtensorMap* map_q, CUtensorMap* map_k, CUtensorMap* map_v, bool* nothing_to_do);
+// A zeroed work-item counter for one launch on `stream` (a slot of a ring of counters inside the library, reset by a
+// memset node ahead of the kernel, so launches on different streams never share one). Defined in fwd.cu.
+int acquire_tile_counter(cudaStream_t stream, int** counter);
 int launch_fwd_256(const b200fa_fwd_args& a, cudaStream_t stream);
 int launch_fwd_512(const b200fa_fwd_args& a, cudaStream_t stream);
 

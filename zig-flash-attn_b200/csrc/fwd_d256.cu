@@ -77,6 +77,8 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t bar_p_full = bar_s_full + 16;        // [2]
   const uint32_t bar_pv_done = bar_p_full + 16;
   const uint32_t tmem_slot = bar_pv_done + 8, abort_slot = tmem_slot + 4;
+  TileQueue tiles;
+  tiles.place(bars + 160);  // the barriers above end at byte 144 with five ring slots
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + (abort_slot - smem_u32(smem_raw)));
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
   const WaitCtx wctx{abort_flag, p.status, nullptr};
@@ -95,6 +97,7 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       mbar_init(bar_p_full + 8 * i, 128);
     }
     mbar_init(bar_pv_done, 1);
+    tiles.init(1 + 4);  // the MMA thread and the four softmax warps
     fence_barrier_init();
   }
   if (warp == 4) {
@@ -140,7 +143,8 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           if (!load_slot(&map_k, part * D, head, row, batch_coord)) return false;
         return true;
       };
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      uint32_t drawn = 0;
+      for (int tile; ok && (tile = tiles.push(drawn, p.tile_counter, num_tiles, wctx)) >= 0;) {
         FwdTile t = decode_tile(p, tile / kSplit, kBlockM);
         const int dh = tile % kSplit;
         if (!t.valid) continue;
@@ -199,7 +203,8 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tc_commit(bar_s_full + 8 * buffer);
         return true;
       };
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      uint32_t popped = 0;
+      for (int tile; ok && (tile = tiles.pop_thread(popped, wctx)) >= 0;) {
         FwdTile t = decode_tile(p, tile / kSplit, kBlockM);
         const int dh = tile % kSplit;
         if (!t.valid) continue;
@@ -242,7 +247,8 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     uint32_t blocks = 0;
     uint32_t s_phase[2] = {0, 0};
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+    uint32_t popped = 0;
+    for (int tile; ok && (tile = tiles.pop_warp(popped, wctx)) >= 0;) {
       FwdTile t = decode_tile(p, tile / kSplit, kBlockM);
       const int dh = tile % kSplit;
       if (!t.valid) continue;

@@ -33,6 +33,7 @@ enum WaitCode : int {
   kWaitBwdCompute = 10,
   kWaitBwdReduce = 11,
   kWaitEpilogue = 12,
+  kWaitTile = 13,
 };
 
 constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // 2 s per wait
