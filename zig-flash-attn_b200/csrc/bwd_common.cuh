@@ -21,6 +21,7 @@ struct BwdParams {
   int64_t dk_batch_stride, dk_row_stride, dk_head_stride;
   int64_t dv_batch_stride, dv_row_stride, dv_head_stride;
   const int2* work_list;  // packed problems: (key sequence, key block) per blockIdx.x
+  int n_blocks, head_slots, section;  // fixed length: decoding of the linear CTA index, see bwd_cta_of
   int* status;
   long long* trace;  // optional cycle counters, null = off
 };
@@ -38,6 +39,27 @@ __device__ __forceinline__ float4 ld_shared_f4(uint32_t addr) {
   float4 v;
   asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
   return v;
+}
+
+// Fixed-length problems launch a one-dimensional grid. CTAs start in index order, so the order decides both the tail of
+// the launch and what runs together: a section of `section` (batch entry, head slot) pairs is walked key block by key
+// block, first (under a causal mask: heaviest) key blocks first, then the next section. The CTAs that run together
+// then read the Q, dO and dQ-accumulator rows of a few heads only, which stay in L2, and the light CTAs of a section
+// fill the tail of its heavy ones.
+struct BwdCta {
+  int seq, n_block, head_slot;
+};
+__device__ __forceinline__ BwdCta bwd_cta_of(const BwdParams& p, int linear) {
+  const int groups = p.prob.batch * p.head_slots;
+  const int per_section = p.section * p.n_blocks;
+  const int s = linear / per_section, r = linear - s * per_section;
+  const int n = imin(p.section, groups - s * p.section);
+  BwdCta c;
+  c.n_block = r / n;
+  const int g = s * p.section + (r - c.n_block * n);
+  c.seq = g / p.head_slots;
+  c.head_slot = g - c.seq * p.head_slots;
+  return c;
 }
 
 // Main kernel for head_dim in (128, 256]: grid.y = 2 * heads_kv (kv head, half of the head dimension).

@@ -5,7 +5,7 @@
 // pass: the accumulators of a 128-key block at 256 columns (dV and dK, 256 TMEM columns each) would fill the tensor
 // memory on their own, so a CTA owns one HALF of the head dimension of its key block: it computes the full scores
 // (reduction over all 256 columns) but accumulates only dV[:, half], dK[:, half] and dQ[:, half]. The two halves of
-// a key block are separate CTAs (blockIdx.y = 2 * kv_head + half).
+// a key block are separate CTAs (head slot = 2 * kv_head + half).
 //
 // Per iteration a CTA takes 64 query rows of one head (a 128-row block of the QueryCursor in two halves):
 //   S^T  = K Q^T            SS-MMA 128x64x256   -> TMEM [0,64)        P^T  = exp2(S^T c - lse)  (BF16, over S^T)
@@ -76,18 +76,21 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                 const __grid_constant__ CUtensorMap map_dq, const __grid_constant__ BwdParams p) {
   const Problem& pr = p.prob;
   // ---- work item (uniform over the CTA; exits before any barrier or TMEM allocation)
-  int seq, n_block;
+  int seq, n_block, head_slot;
   if (p.work_list) {
     const int2 e = p.work_list[blockIdx.x];
     seq = e.x;
     n_block = e.y;
+    head_slot = blockIdx.y;
     if (seq >= pr.batch) return;
   } else {
-    seq = blockIdx.z;
-    n_block = blockIdx.x;
+    const BwdCta cta = bwd_cta_of(p, blockIdx.x);
+    seq = cta.seq;
+    n_block = cta.n_block;
+    head_slot = cta.head_slot;
   }
-  const int kv_head = blockIdx.y >> 1;
-  const int dh = blockIdx.y & 1;  // half of the head dimension owned by this CTA
+  const int kv_head = head_slot >> 1;
+  const int dh = head_slot & 1;  // half of the head dimension owned by this CTA
   const SeqInfo s = seq_info(pr, seq);
   const int n0 = n_block * kBlockN;
   if (n0 >= s.lk) return;
