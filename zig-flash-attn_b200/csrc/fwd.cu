@@ -40,8 +40,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
            const __grid_constant__ CUtensorMap map_v, const __grid_constant__ FwdParams p) {
   using Cfg = FwdConfig<D>;
   constexpr int NS = Cfg::kStages;
-  // Register split between the warpgroups: 2 x 128 x 208 + 128 x 88 = 64512, the 384 x 168 registers the CTA is launched with (setmaxnreg only moves registers inside that pool).
-  constexpr int kRegsSoftmax = 208, kRegsOther = 88;
+  // Register split between the warpgroups: 2 x 128 x 200 + 128 x 104 = 64512, the 384 x 168 registers the CTA is
+  // launched with (setmaxnreg only moves registers inside that pool). With 208 / 88 the MMA and TMA warps spilled.
+  constexpr int kRegsSoftmax = 200, kRegsOther = 104;
   // Of every kPolyPeriod pairs of scores, kPolyCount take the polynomial exp2 and the rest the MUFU.
   constexpr int kPolyPeriod = 4, kPolyCount = 0;
   // Keep all 128 scores of a row in registers (true) or read the lower half from TMEM a second time (false).
