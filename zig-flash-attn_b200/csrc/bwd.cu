@@ -14,6 +14,9 @@
 //                                    and added into the FP32 dQ accumulator with TMA reduce-add.
 // Warps 0-7 compute P and dS (two groups of four warps, 64 query columns each), warps 8-11 drain dQ, warp 12 issues
 // MMAs, warp 13 issues TMA loads and the asynchronous copies of the per-row statistics.
+// Per iteration the MMA warp issues dV, S^T of the next iteration, then dQ before dK (the drain of dQ gates the next
+// dP^T, which uses the same TMEM columns), then dP^T of the next iteration. The CTAs of a fixed-length problem are
+// ordered by bwd_cta_of (bwd_common.cuh); packed problems take their (sequence, key block) from the work list.
 #include <limits.h>
 
 #include "bwd_common.cuh"

@@ -4,12 +4,14 @@
 // persistent inter-sequence forward (zig/inter_sequence_forward_sm100.zig:40-1274); one kernel serves fixed-length,
 // packed (varlen) and inter-sequence problems because key blocks come from the KeyCursor of attn_index.h.
 //
-// One persistent CTA per SM. A work item is 256 query rows of one head (two 128-row MMA tiles, "stages").
+// One persistent CTA per SM; the CTAs draw work items from a global counter (TileQueue). A work item is 256 query rows
+// of one head (two 128-row MMA tiles, "stages").
 // Warp roles: warps 0-3 softmax of stage 0, warps 4-7 softmax of stage 1 (one thread per query row, TMEM lane =
 // row), warp 8 issues tcgen05 MMAs, warp 9 issues TMA loads.
 //   S_i = Q_i K_j^T   SS-MMA 128x128xD  into TMEM columns [128 i, 128 i + 128)
-//   P_i               BF16, written by the softmax warps over the first 64 columns of S_i
-//   O_i += P_i V_j    TS-MMA 128xDx128 (A from TMEM) into TMEM columns [256 + D i, 256 + D i + D)
+//   P_i               BF16, written by the softmax warps over columns [64,128) of S_i (whose scores they hold in registers)
+//   O_i += P_i V_j    TS-MMA 128xDx128 (A from TMEM) into TMEM columns [256 + D i, 256 + D i + D), issued in two key
+//                     halves: keys [64,128) as soon as their probabilities are stored, keys [0,64) after the rest
 // Q tiles, and a ring of K/V tiles, are TMA-loaded into 128-byte swizzled shared memory and tracked by mbarriers.
 // Softmax runs in the log2 domain with a lazy rescale: the running reference maximum only moves when the block
 // maximum exceeds it by more than 8 (in log2 units), so O is almost never rescaled (reference
