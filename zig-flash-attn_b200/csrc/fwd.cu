@@ -487,7 +487,8 @@ int acquire_tile_counter(cudaStream_t stream, int** counter) {
 }
 
 int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim, int tile_rows, int kv_box_rows,
-                    FwdParams* params, CUtensorMap* map_q, CUtensorMap* map_k, CUtensorMap* map_v, bool* nothing_to_do) {
+                    FwdParams* params, CUtensorMap* map_q, CUtensorMap* map_k, CUtensorMap* map_v, bool* nothing_to_do,
+                    int v_box_rows) {
   const b200fa_problem& bp = a.problem;
   const int D = bp.head_dim;  // columns of the tensors; `head_dim` is the width the kernel is compiled for
   (void)head_dim;
@@ -545,7 +546,8 @@ int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim,
   if (status != B200FA_OK) return status;
   status = encode_tensor_map(map_v, v_base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, no_keys ? 1 : bp.heads_kv, k_rows,
                              tensor_batch, no_keys ? D : a.v_stride[2], no_keys ? D : a.v_stride[1],
-                             no_keys ? D : (packed ? k_rows * a.v_stride[1] : a.v_stride[0]), 64, kv_box_rows);
+                             no_keys ? D : (packed ? k_rows * a.v_stride[1] : a.v_stride[0]), 64,
+                             v_box_rows > 0 ? v_box_rows : kv_box_rows);
   if (status != B200FA_OK) return status;
   status = acquire_tile_counter(stream, &p.tile_counter);
   if (status != B200FA_OK) return status;

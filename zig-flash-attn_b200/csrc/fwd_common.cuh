@@ -116,7 +116,8 @@ __device__ __forceinline__ FwdTile decode_tile(const FwdParams& p, int tile, int
 // `tile_rows` = query rows per work item, `kv_box_rows` = key rows per TMA box. Sets *nothing_to_do when no kernel is
 // needed. Defined in fwd.cu.
 int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim, int tile_rows, int kv_box_rows,
-                    FwdParams* p, CUtensorMap* map_q, CUtensorMap* map_k, CUtensorMap* map_v, bool* nothing_to_do);
+                    FwdParams* p, CUtensorMap* map_q, CUtensorMap* map_k, CUtensorMap* map_v, bool* nothing_to_do,
+                    int v_box_rows = 0 /* rows per TMA box of V when they differ from those of K */);
 // A zeroed work-item counter for one launch on `stream` (a slot of a ring of counters inside the library, reset by a
 // memset node ahead of the kernel, so launches on different streams never share one). Defined in fwd.cu.
 int acquire_tile_counter(cudaStream_t stream, int** counter);

@@ -1,84 +1,57 @@
-// Forward attention kernel for head_dim 256 on sm_100a (the reference builds head_dim 256 forward as a 2-CTA variant
-// of zig/flash_fwd_sm100.zig, zig/configurations.zig:1567-1574; this is a single-CTA design).
+// Forward attention kernel for head_dim 256 on sm_100a with 128-key blocks (the reference builds head_dim 256 forward
+// as a 2-CTA variant of zig/flash_fwd_sm100.zig, zig/configurations.zig:1567-1574; this is a single-CTA design).
 //
-// With 256 output columns the FP32 accumulator O takes half of TMEM, so there is one query stage: a work item is 128
-// query rows of one head. Keys are taken 64 at a time, and the score tile S (128 x 64) is double-buffered instead:
-//   S(n)   = Q K_n^T     SS-MMA 128x64x256  -> TMEM buffer n & 1, columns [128 b, 128 b + 64)
-//   P(n)                 BF16, columns [128 b + 64, 128 b + 96) of the same buffer (no aliasing with S)
-//   O     += P(n) V_n    TS-MMA 128x256x64  -> TMEM columns [256, 512)
-// The MMA warp issues S(n + 2) right after O += P(n) V_n, so while the softmax warps work on block n + 1 the tensor pipe
-// runs the PV product of block n and the scores of block n + 2. Per block the tensor work (2 x 512 cycles) about equals
-// the softmax work of one warpgroup, which is why one softmax warpgroup is enough here.
+// A key block has 128 keys, so the score MMA is 128 x 128 x 16 (8 KB of operands for 64 cycles of tensor work) like in
+// the head_dim 128 kernel; with 64-key blocks (the kernel of fwd_d512.cu, which served head_dim 256 before) a
+// 128 x 64 x 16 MMA reads 6 KB for 32 cycles and the score product is bound by shared-memory bandwidth (1010 against
+// 1290 TF/s on batch 4, seqlen 8192, heads 16/4, causal):
+//   S(n)   = Q K_n^T     SS-MMA 128x128x256 -> TMEM buffer n & 1, columns [128 b, 128 b + 128)
+//   P(n)                 BF16, over columns [64,128) of the same buffer (whose scores the softmax warps hold in registers)
+//   O     += P(n) V_n    TS-MMA 128x256x128 -> TMEM columns [256, 512), issued in two key halves
+// One 128-row query stage with the score tile double-buffered: the MMA warp issues S(n + 2) right after O += P(n) V_n, so
+// the softmax of block n + 1 overlaps the PV product of block n and the scores of block n + 2.
+// Shared memory: Q 64 KB, one K slot of 64 KB (128 keys x 256 columns; the next K block is loaded as soon as the score
+// MMA of the current one has completed) and a ring of three V slots of 32 KB (64 keys x 256 columns each).
 // Warps 0-3: softmax and epilogue (thread = query row), warp 4: MMA issue, warp 5: TMA loads, warps 6-7: spare.
-//
-// head_dim 512 (kSplit = 2) runs the same kernel: an accumulator of 512 columns would take all of TMEM, so a work
-// item is split in two, one per 256 output columns (tile index = 2 * item + half). Both halves compute the full
-// scores (reduction over 512 columns: a key block is two ring slots) and their own half of P V. The query tile takes
-// 128 KB of shared memory, which leaves three ring slots.
 #include "fwd_common.cuh"
 
 namespace b200fa {
 
 namespace d256 {
-constexpr int D = 256;                            // output columns of a CTA; the reduction runs over kSplit * D columns
-constexpr int kSubN = 64;                         // keys per block
-constexpr int kKvBytes = kSubN * D * 2;           // 32 KB: one ring slot (64 keys x 256 columns)
-constexpr int kQPanel = kBlockM * 128;            // 64-column panel of Q
-constexpr int kKvPanel = kSubN * 128;             // 64-column panel of K / V
+constexpr int D = 256;
+constexpr int kVSlots = 3;                        // ring of V half-blocks
+constexpr int kQBytes = kBlockM * D * 2;          // 64 KB
+constexpr int kKBytes = kBlockN * D * 2;          // 64 KB
+constexpr int kVBytes = 64 * D * 2;               // 32 KB: 64 keys
+constexpr int kQPanel = kBlockM * 128;            // 64-column panel of Q (128 rows)
+constexpr int kKPanel = kBlockN * 128;            // 64-column panel of K (128 rows)
+constexpr int kVPanel = 64 * 128;                 // 64-column panel of a V half-block (64 rows)
+constexpr int kSmemBytes = kQBytes + kKBytes + kVSlots * kVBytes + 1024 + 512;
 constexpr int kThreads = 256;
 constexpr int kTmemO = 256;
-template <int kSplit>
-struct Config {
-  static constexpr int kStages = kSplit == 1 ? 5 : 3;            // K/V ring slots
-  static constexpr int kQBytes = kBlockM * D * kSplit * 2;       // 64 KB or 128 KB
-  static constexpr int kSmemBytes = kQBytes + kStages * kKvBytes + 1024 + 256;
-  static_assert(kSmemBytes <= 232448, "shared memory exceeds the per-CTA limit");
-};
+static_assert(kSmemBytes <= 232448, "shared memory exceeds the per-CTA limit");
 }  // namespace d256
 
-// Yields the key blocks of a KeyCursor as 64-key halves.
-struct SubBlockCursor {
-  KeyCursor cursor;
-  OtherBlock block;
-  int half;
-  __device__ void init(const Problem* problem, int seq, const SeqInfo& s, int m0, int m1) {
-    cursor.init(problem, seq, s, m0, m1);
-    half = 2;
-  }
-  __device__ bool next(OtherBlock* out) {
-    if (half >= 2) {
-      if (!cursor.next(&block)) return false;
-      half = 0;
-    }
-    *out = block;
-    out->row = block.row + half * d256::kSubN;
-    out->col0 = block.col0 + half * d256::kSubN;
-    ++half;
-    return true;
-  }
-};
-
-template <int kSplit>
 __global__ void __launch_bounds__(d256::kThreads, 1)
 fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ FwdParams p) {
+                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ FwdParams p) {
   using namespace d256;
-  constexpr int NS = Config<kSplit>::kStages;
-  constexpr int kQBytes = Config<kSplit>::kQBytes;
-  const int num_tiles = p.num_tiles * kSplit;  // tile = kSplit * work item + half of the output columns
+  constexpr int NV = kVSlots;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t smem_q = smem_base;
-  const uint32_t smem_kv = smem_base + kQBytes;
-  const uint32_t bars = smem_kv + NS * kKvBytes;
-  const uint32_t bar_q_full = bars, bar_q_empty = bars + 8;
-  const uint32_t bar_kv_full = bars + 16, bar_kv_empty = bar_kv_full + 8 * NS;
-  const uint32_t bar_s_full = bar_kv_empty + 8 * NS;  // [2]
-  const uint32_t bar_p_full = bar_s_full + 16;        // [2]
+  const uint32_t smem_k = smem_q + kQBytes;
+  const uint32_t smem_v = smem_k + kKBytes;
+  const uint32_t bars = smem_v + NV * kVBytes;
+  const uint32_t bar_q_full = bars, bar_q_empty = bars + 8, bar_k_full = bars + 16, bar_k_empty = bars + 24;
+  const uint32_t bar_v_full = bars + 32, bar_v_empty = bar_v_full + 8 * NV;  // [NV] each
+  const uint32_t bar_s_full = bar_v_empty + 8 * NV;                          // [2]
+  const uint32_t bar_p_half = bar_s_full + 16;                               // [2]
+  const uint32_t bar_p_full = bar_p_half + 16;                               // [2]
   const uint32_t bar_pv_done = bar_p_full + 16;
   const uint32_t tmem_slot = bar_pv_done + 8, abort_slot = tmem_slot + 4;
   TileQueue tiles;
-  tiles.place(bars + 160);  // the barriers above end at byte 144 with five ring slots
+  tiles.place(bars + 256);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + (abort_slot - smem_u32(smem_raw)));
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
   const WaitCtx wctx{abort_flag, p.status, nullptr};
@@ -88,12 +61,15 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     *abort_flag = 0;
     mbar_init(bar_q_full, 1);
     mbar_init(bar_q_empty, 1);
-    for (int i = 0; i < NS; ++i) {
-      mbar_init(bar_kv_full + 8 * i, 1);
-      mbar_init(bar_kv_empty + 8 * i, 1);
+    mbar_init(bar_k_full, 1);
+    mbar_init(bar_k_empty, 1);
+    for (int i = 0; i < NV; ++i) {
+      mbar_init(bar_v_full + 8 * i, 1);
+      mbar_init(bar_v_empty + 8 * i, 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_s_full + 8 * i, 1);
+      mbar_init(bar_p_half + 8 * i, 128);
       mbar_init(bar_p_full + 8 * i, 128);
     }
     mbar_init(bar_pv_done, 1);
@@ -110,9 +86,9 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t tmem_base = *tmem_ptr_smem;
   const Problem& pr = p.prob;
 
-  // Number of 64-key blocks of a work item (every role needs it to know where the pipeline ends).
+  // Number of key blocks of a work item (every role needs it to know where the pipeline ends).
   auto count_blocks = [&](const FwdTile& t) {
-    SubBlockCursor cur;
+    KeyCursor cur;
     cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kBlockM, t.s.lq));
     OtherBlock kb;
     int n = 0;
@@ -122,35 +98,34 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   if (warp == 5) {
     // ------------------------------------------------------------------ TMA producer
-    // Load order = consumption order of the MMA warp: K0, K1, then V(n), K(n + 2) for n = 0, 1, ...
+    // Load order = consumption order of the MMA warp: K0, K1, then V_hi(n), V_lo(n), K(n + 2) for n = 0, 1, ...
     if (lane == 0) {
-      uint32_t ring = 0, q_count = 0;
+      uint32_t k_count = 0, v_count = 0, q_count = 0, drawn = 0;
       bool ok = true;
-      // One ring slot: 64 rows x 256 columns starting at column col0.
-      auto load_slot = [&](const CUtensorMap* map, int col0, int head, int row, int batch_coord) -> bool {
-        const uint32_t slot = ring % NS, phase = (ring / NS) & 1;
-        if (!mbar_wait(bar_kv_empty + 8 * slot, phase ^ 1, wctx, kWaitKvEmpty)) return false;
-        const uint32_t bar = bar_kv_full + 8 * slot;
-        mbar_expect_tx(bar, kKvBytes);
+      auto load_k = [&](int head, int row, int batch_coord) -> bool {
+        if (!mbar_wait(bar_k_empty, (k_count & 1) ^ 1, wctx, kWaitKvEmpty)) return false;
+        mbar_expect_tx(bar_k_full, kKBytes);
 #pragma unroll
-        for (int h = 0; h < 4; ++h)
-          tma_load_4d(smem_kv + slot * kKvBytes + h * kKvPanel, map, bar, col0 + h * 64, head, row, batch_coord);
-        ++ring;
+        for (int h = 0; h < 4; ++h) tma_load_4d(smem_k + h * kKPanel, &map_k, bar_k_full, h * 64, head, row, batch_coord);
+        ++k_count;
         return true;
       };
-      auto load_k = [&](int head, int row, int batch_coord) -> bool {  // all reduction columns: kSplit slots
-        for (int part = 0; part < kSplit; ++part)
-          if (!load_slot(&map_k, part * D, head, row, batch_coord)) return false;
+      auto load_v_half = [&](int head, int row, int batch_coord) -> bool {  // 64 keys starting at `row`
+        const uint32_t slot = v_count % NV, phase = (v_count / NV) & 1;
+        if (!mbar_wait(bar_v_empty + 8 * slot, phase ^ 1, wctx, kWaitKvEmpty)) return false;
+        const uint32_t bar = bar_v_full + 8 * slot;
+        mbar_expect_tx(bar, kVBytes);
+#pragma unroll
+        for (int h = 0; h < 4; ++h) tma_load_4d(smem_v + slot * kVBytes + h * kVPanel, &map_v, bar, h * 64, head, row, batch_coord);
+        ++v_count;
         return true;
       };
-      uint32_t drawn = 0;
-      for (int tile; ok && (tile = tiles.push(drawn, p.tile_counter, num_tiles, wctx)) >= 0;) {
-        FwdTile t = decode_tile(p, tile / kSplit, kBlockM);
-        const int dh = tile % kSplit;
+      for (int tile; ok && (tile = tiles.push(drawn, p.tile_counter, p.num_tiles, wctx)) >= 0;) {
+        FwdTile t = decode_tile(p, tile, kBlockM);
         if (!t.valid) continue;
         const int n_blocks = count_blocks(t);
         if (n_blocks == 0) continue;
-        SubBlockCursor cur_k, cur_v;
+        KeyCursor cur_k, cur_v;
         cur_k.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kBlockM, t.s.lq));
         cur_v.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kBlockM, t.s.lq));
         OtherBlock kb;
@@ -158,7 +133,7 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         ++q_count;
         mbar_expect_tx(bar_q_full, kQBytes);
 #pragma unroll
-        for (int h = 0; h < 4 * kSplit; ++h)
+        for (int h = 0; h < 4; ++h)
           tma_load_4d(smem_q + h * kQPanel, &map_q, bar_q_full, h * 64, t.head, t.s.q0 + t.m0, t.s.batch_coord);
         for (int i = 0; ok && i < imin(2, n_blocks); ++i) {
           cur_k.next(&kb);
@@ -166,7 +141,7 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         for (int n = 0; ok && n < n_blocks; ++n) {
           cur_v.next(&kb);
-          ok = load_slot(&map_v, dh * D, t.kv_head, kb.row, t.s.batch_coord);
+          ok = load_v_half(t.kv_head, kb.row + 64, t.s.batch_coord) && load_v_half(t.kv_head, kb.row, t.s.batch_coord);
           if (ok && n + 2 < n_blocks) {
             cur_k.next(&kb);
             ok = load_k(t.kv_head, kb.row, t.s.batch_coord);
@@ -177,61 +152,58 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   } else if (warp == 4) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc_bf16(kBlockM, kSubN, 0, 0);
+      constexpr uint32_t idesc_s = umma_idesc_bf16(kBlockM, kBlockN, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(kBlockM, D, 0, 1);
-      uint32_t ring = 0, q_count = 0, blocks = 0;  // blocks: PV products issued so far (all work items)
+      uint32_t k_count = 0, v_count = 0, q_count = 0, popped = 0;
       uint32_t p_phase[2] = {0, 0};
       bool ok = true;
-      auto wait_kv = [&](uint32_t index) -> bool {
-        return mbar_wait(bar_kv_full + 8 * (index % NS), (index / NS) & 1, wctx, kWaitKvFull);
-      };
-      // S = Q K^T over the kSplit ring slots of a key block; each slot is released as soon as its MMAs are issued.
+      // S = Q K^T into score buffer `buffer`; the K slot is released when these MMAs have completed.
       auto issue_s = [&](int buffer) -> bool {
-        for (int part = 0; part < kSplit; ++part) {
-          const uint32_t k_index = ring++;
-          if (!wait_kv(k_index)) return false;
-          tc_fence_after();
-          const uint32_t k_smem = smem_kv + (k_index % NS) * kKvBytes;
-          const uint32_t q_smem = smem_q + part * 4 * kQPanel;
+        if (!mbar_wait(bar_k_full, k_count & 1, wctx, kWaitKvFull)) return false;
+        ++k_count;
+        tc_fence_after();
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            umma_ss(tmem_base + buffer * 128, umma_smem_desc(q_smem + (kk >> 2) * kQPanel + (kk & 3) * 32, 16, 1024),
-                    umma_smem_desc(k_smem + (kk >> 2) * kKvPanel + (kk & 3) * 32, 16, 1024), idesc_s, part > 0 || kk > 0);
-          }
-          tc_commit(bar_kv_empty + 8 * (k_index % NS));
+        for (int kk = 0; kk < D / 16; ++kk) {
+          umma_ss(tmem_base + buffer * 128, umma_smem_desc(smem_q + (kk >> 2) * kQPanel + (kk & 3) * 32, 16, 1024),
+                  umma_smem_desc(smem_k + (kk >> 2) * kKPanel + (kk & 3) * 32, 16, 1024), idesc_s, kk > 0);
         }
+        tc_commit(bar_k_empty);
         tc_commit(bar_s_full + 8 * buffer);
         return true;
       };
-      uint32_t popped = 0;
+      // O += P[:, 64 h .. 64 h + 64) V_half: the next V slot of the ring holds those 64 keys.
+      auto issue_pv_half = [&](int buffer, int half, bool accumulate) -> bool {
+        const uint32_t slot = v_count % NV, phase = (v_count / NV) & 1;
+        if (!mbar_wait(bar_v_full + 8 * slot, phase, wctx, kWaitKvFull)) return false;
+        ++v_count;
+        tc_fence_after();
+        const uint32_t v_smem = smem_v + slot * kVBytes;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          umma_ts(tmem_base + kTmemO, tmem_base + buffer * 128 + 64 + (4 * half + kk) * 8,
+                  umma_smem_desc(v_smem + kk * 2048, kVPanel, 1024), idesc_pv, accumulate || kk > 0);
+        }
+        tc_commit(bar_v_empty + 8 * slot);
+        return true;
+      };
       for (int tile; ok && (tile = tiles.pop_thread(popped, wctx)) >= 0;) {
-        FwdTile t = decode_tile(p, tile / kSplit, kBlockM);
-        const int dh = tile % kSplit;
+        FwdTile t = decode_tile(p, tile, kBlockM);
         if (!t.valid) continue;
         const int n_blocks = count_blocks(t);
         if (n_blocks == 0) continue;
         const uint32_t q_phase = q_count & 1;
         ++q_count;
         if (!mbar_wait(bar_q_full, q_phase, wctx, kWaitQFull)) { ok = false; break; }
-        // The S buffers alternate with the block index of the work item; their barrier phases count per buffer.
         for (int i = 0; ok && i < imin(2, n_blocks); ++i) ok = issue_s(i);
         for (int n = 0; ok && n < n_blocks; ++n) {
           const int buffer = n & 1;
-          const uint32_t v_index = ring++;
-          if (!wait_kv(v_index)) { ok = false; break; }
-          // phase of p_full[buffer]: number of earlier blocks that used this buffer
+          // keys [64,128) first: their probabilities are stored first
+          if (!mbar_wait(bar_p_half + 8 * buffer, p_phase[buffer], wctx, kWaitPFull)) { ok = false; break; }
+          if (!issue_pv_half(buffer, 1, n > 0)) { ok = false; break; }
           if (!mbar_wait(bar_p_full + 8 * buffer, p_phase[buffer], wctx, kWaitPFull)) { ok = false; break; }
           p_phase[buffer] ^= 1;
-          tc_fence_after();
-          const uint32_t v_smem = smem_kv + (v_index % NS) * kKvBytes;
-#pragma unroll
-          for (int kk = 0; kk < kSubN / 16; ++kk) {
-            umma_ts(tmem_base + kTmemO, tmem_base + buffer * 128 + 64 + kk * 8,
-                    umma_smem_desc(v_smem + kk * 2048, kKvPanel, 1024), idesc_pv, n > 0 || kk > 0);
-          }
+          if (!issue_pv_half(buffer, 0, true)) { ok = false; break; }
           tc_commit(bar_pv_done);
-          tc_commit(bar_kv_empty + 8 * (v_index % NS));
-          ++blocks;
           if (n + 2 < n_blocks) ok = issue_s(buffer);
         }
         if (ok) tc_commit(bar_q_empty);
@@ -244,18 +216,16 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     const uint32_t t_o = tmem_base + lane_addr + kTmemO;
     const float scale_log2 = p.scale_log2;
-    uint32_t blocks = 0;
+    uint32_t blocks = 0, popped = 0;
     uint32_t s_phase[2] = {0, 0};
     bool ok = true;
-    uint32_t popped = 0;
     for (int tile; ok && (tile = tiles.pop_warp(popped, wctx)) >= 0;) {
-      FwdTile t = decode_tile(p, tile / kSplit, kBlockM);
-      const int dh = tile % kSplit;
+      FwdTile t = decode_tile(p, tile, kBlockM);
       if (!t.valid) continue;
       const int row = t.m0 + row_in_tile;
-      SubBlockCursor cur;
+      KeyCursor cur;
       cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kBlockM, t.s.lq));
-      const int band_lo = cur.cursor.band.lo(row), band_hi = cur.cursor.band.hi(row);
+      const int band_lo = cur.band.lo(row), band_hi = cur.band.hi(row);
       float m = -INFINITY, l = 0.f;
       int tile_blocks = 0;
       OtherBlock kb;
@@ -265,10 +235,6 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (!mbar_wait_warp(bar_s_full + 8 * buffer, s_phase[buffer], wctx, kWaitSFull)) { ok = false; break; }
         s_phase[buffer] ^= 1;
         tc_fence_after();
-        float2 s[32];  // 64 scores
-        tmem_ld32(t_s, reinterpret_cast<uint32_t*>(s));
-        tmem_ld32(t_s + 32, reinterpret_cast<uint32_t*>(s) + 32);
-        tc_wait_ld();
         int lo, hi;
         if (kb.banded) {
           lo = band_lo - kb.col0;
@@ -277,23 +243,40 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           lo = 0;
           hi = kb.limit - kb.col0;
         }
-        if (__any_sync(0xffffffffu, lo > 0 || hi < kSubN)) {
+        const bool masked = __any_sync(0xffffffffu, lo > 0 || hi < kBlockN);
+        auto apply_mask = [&](float2* values, int first_column) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            s[i].x = (2 * i >= lo && 2 * i < hi) ? s[i].x : -INFINITY;
-            s[i].y = (2 * i + 1 >= lo && 2 * i + 1 < hi) ? s[i].y : -INFINITY;
+            const int c = first_column + 2 * i;
+            values[i].x = (c >= lo && c < hi) ? values[i].x : -INFINITY;
+            values[i].y = (c + 1 >= lo && c + 1 < hi) ? values[i].y : -INFINITY;
           }
-        }
-        float bm0 = fmaxf(s[0].x, s[0].y), bm1 = fmaxf(s[1].x, s[1].y);
-        float bm2 = fmaxf(s[2].x, s[2].y), bm3 = fmaxf(s[3].x, s[3].y);
+        };
+        auto max_of = [&](const float2* values) {
+          float a = fmaxf(values[0].x, values[0].y), b = fmaxf(values[1].x, values[1].y);
+          float c = fmaxf(values[2].x, values[2].y), d = fmaxf(values[3].x, values[3].y);
 #pragma unroll
-        for (int i = 4; i < 32; i += 4) {
-          bm0 = fmaxf(bm0, fmaxf(s[i].x, s[i].y));
-          bm1 = fmaxf(bm1, fmaxf(s[i + 1].x, s[i + 1].y));
-          bm2 = fmaxf(bm2, fmaxf(s[i + 2].x, s[i + 2].y));
-          bm3 = fmaxf(bm3, fmaxf(s[i + 3].x, s[i + 3].y));
-        }
-        const float m_new = fmaxf(m, fmaxf(fmaxf(bm0, bm1), fmaxf(bm2, bm3)));
+          for (int i = 4; i < 32; i += 4) {
+            a = fmaxf(a, fmaxf(values[i].x, values[i].y));
+            b = fmaxf(b, fmaxf(values[i + 1].x, values[i + 1].y));
+            c = fmaxf(c, fmaxf(values[i + 2].x, values[i + 2].y));
+            d = fmaxf(d, fmaxf(values[i + 3].x, values[i + 3].y));
+          }
+          return fmaxf(fmaxf(a, b), fmaxf(c, d));
+        };
+        // Pass 1: row maximum. Columns [0,64) are read for the maximum only and read again in pass 2; columns
+        // [64,128) stay in registers, because P goes over them.
+        float2 low[32], high[32];
+        tmem_ld32(t_s, reinterpret_cast<uint32_t*>(low));
+        tmem_ld32(t_s + 32, reinterpret_cast<uint32_t*>(low) + 32);
+        tc_wait_ld();
+        if (masked) apply_mask(low, 0);
+        const float max_low = max_of(low);
+        tmem_ld32(t_s + 64, reinterpret_cast<uint32_t*>(high));
+        tmem_ld32(t_s + 96, reinterpret_cast<uint32_t*>(high) + 32);
+        tc_wait_ld();
+        if (masked) apply_mask(high, 64);
+        const float m_new = fmaxf(m, fmaxf(max_low, max_of(high)));
         const bool grow = (m_new - m) * scale_log2 > 8.f;  // also true when m is -inf and m_new is finite
         if (__any_sync(0xffffffffu, grow)) {
           float alpha = 1.f;
@@ -320,24 +303,37 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const float mc = (m == -INFINITY) ? 0.f : m * scale_log2;
         const float2 scale2 = make_float2(scale_log2, scale_log2), shift2 = make_float2(-mc, -mc);
         float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
+        // 64 scores -> 64 probabilities (BF16) stored at P columns [first_p_column, first_p_column + 32)
+        auto exponentiate = [&](const float2* values, uint32_t first_p_column) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t packed[16];
+          for (int c = 0; c < 2; ++c) {
+            uint32_t packed[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float2 x = __ffma2_rn(s[16 * c + i], scale2, shift2);
-            float2 e;
-            e.x = ex2_approx(x.x);
-            e.y = ex2_approx(x.y);
-            if (i & 1) sum_b = __fadd2_rn(sum_b, e); else sum_a = __fadd2_rn(sum_a, e);
-            packed[i] = pack_bf16x2(e.x, e.y);
+            for (int i = 0; i < 16; ++i) {
+              const float2 x = __ffma2_rn(values[16 * c + i], scale2, shift2);
+              float2 e;
+              e.x = ex2_approx(x.x);
+              e.y = ex2_approx(x.y);
+              if (i & 1) sum_b = __fadd2_rn(sum_b, e); else sum_a = __fadd2_rn(sum_a, e);
+              packed[i] = pack_bf16x2(e.x, e.y);
+            }
+            tmem_st16(t_s + 64 + first_p_column + 16 * c, packed);
           }
-          tmem_st16(t_s + 64 + 16 * c, packed);
-        }
+        };
+        // Pass 2 for columns [0,64): the loads are in flight while the upper half is exponentiated.
+        tmem_ld32(t_s, reinterpret_cast<uint32_t*>(low));
+        tmem_ld32(t_s + 32, reinterpret_cast<uint32_t*>(low) + 32);
+        exponentiate(high, 32);
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_p_half + 8 * buffer);  // keys [64,128): their half of the PV product may start
+        tc_wait_ld();
+        if (masked) apply_mask(low, 0);
+        exponentiate(low, 0);
         l += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
-        // Observe the PV product of the previous block before releasing this one. The scores of block n only prove
-        // that PV(n - 2) has completed, so without this wait the barrier could be two completions away from the one
-        // the epilogue waits for, which a parity wait cannot tell apart from "done".
+        // Observe the PV product of the previous block before releasing this one: the scores of block n only prove that
+        // PV(n - 2) has completed, and a parity wait cannot tell a barrier that is two completions behind from one that
+        // is done.
         if (tile_blocks > 0 && !mbar_wait_warp(bar_pv_done, (blocks - 1) & 1, wctx, kWaitPvDone)) { ok = false; break; }
         tc_wait_st();
         tc_fence_before();
@@ -349,14 +345,14 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // ---- epilogue
       const bool row_valid = row < t.s.lq;
       __nv_bfloat16* o_row = p.o + t.s.batch_coord * p.o_batch_stride + (int64_t)(t.s.q0 + row) * p.o_row_stride +
-                             (int64_t)t.head * p.o_head_stride + dh * D;
+                             (int64_t)t.head * p.o_head_stride;
       float* lse_ptr = p.lse + t.s.batch_coord * p.lse_batch_stride + (int64_t)t.head * p.lse_head_stride + t.s.q0 + row;
       if (tile_blocks == 0) {
         if (row_valid) {
           const uint4 zero = make_uint4(0, 0, 0, 0);
 #pragma unroll
           for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(o_row)[c] = zero;
-          if (dh == 0) *lse_ptr = -INFINITY;
+          *lse_ptr = -INFINITY;
         }
         continue;
       }
@@ -380,7 +376,7 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
         }
       }
-      if (row_valid && dh == 0) {  // both halves hold the same statistics
+      if (row_valid) {
         const float mc = (m == -INFINITY) ? 0.f : m * scale_log2;
         *lse_ptr = l > 0.f ? (mc + log2f(l)) * 0.69314718055994531f : -INFINITY;
       }
@@ -398,28 +394,22 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (warp == 4) tmem_dealloc(tmem_base, 512);
 }
 
-template <int kSplit>
-static int launch_fwd_wide(const b200fa_fwd_args& a, cudaStream_t stream) {
-  using Cfg = d256::Config<kSplit>;
+int launch_fwd_256(const b200fa_fwd_args& a, cudaStream_t stream) {
   FwdParams p;
   CUtensorMap map_q, map_k, map_v;
   bool nothing_to_do = false;
-  int status = prepare_forward(a, stream, d256::D * kSplit, kBlockM, d256::kSubN, &p, &map_q, &map_k, &map_v, &nothing_to_do);
+  int status = prepare_forward(a, stream, d256::D, kBlockM, kBlockN, &p, &map_q, &map_k, &map_v, &nothing_to_do, 64);
   if (status != B200FA_OK || nothing_to_do) return status;
   static bool attribute_set[64] = {false};
-  status = set_dynamic_smem_once(reinterpret_cast<const void*>(&fwd_d256_kernel<kSplit>), Cfg::kSmemBytes, attribute_set);
+  status = set_dynamic_smem_once(reinterpret_cast<const void*>(&fwd_d256_kernel), d256::kSmemBytes, attribute_set);
   if (status != B200FA_OK) return status;
   int sms = 0;
   status = device_sm_count(&sms);
   if (status != B200FA_OK) return status;
-  const int tiles = p.num_tiles * kSplit;
-  const int grid = tiles < sms ? tiles : sms;
-  fwd_d256_kernel<kSplit><<<grid, d256::kThreads, Cfg::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+  const int grid = p.num_tiles < sms ? p.num_tiles : sms;
+  fwd_d256_kernel<<<grid, d256::kThreads, d256::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
   B200FA_CUDA_CHECK(cudaGetLastError());
   return B200FA_OK;
 }
-
-int launch_fwd_256(const b200fa_fwd_args& a, cudaStream_t stream) { return launch_fwd_wide<1>(a, stream); }
-int launch_fwd_512(const b200fa_fwd_args& a, cudaStream_t stream) { return launch_fwd_wide<2>(a, stream); }
 
 }  // namespace b200fa
