@@ -518,96 +518,75 @@ __device__ __forceinline__ bool locate_row(const RowMap& m, int64_t row, int* ba
   return true;
 }
 
-// One warp per (row, head): dpsum = -sum_d O dO, lse_log2 = -lse log2(e), dq_accum row = 0.
+// Both kernels below are HBM-bound streams. A lane handles 8 columns (16 bytes of BF16, 32 bytes of FP32), so a row of
+// D columns takes D / 8 lanes and a warp handles 256 / D rows at once; a block of 256 threads covers kPrePostRows rows.
+template <int D>
+struct PrePost {
+  static constexpr int kLanesPerRow = D / 8;
+  static constexpr int kRowsPerWarp = 32 / kLanesPerRow;
+  static constexpr int kRowsPerBlock = 8 * kRowsPerWarp;
+};
+
+// dpsum = -sum_d O dO, lse_log2 = -lse log2(e), dq_accum row = 0 (reference zig/flash_bwd_preprocess.zig:118-237).
 template <int D>
 __global__ void __launch_bounds__(256) bwd_preprocess_kernel(
     const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout, const float* __restrict__ lse,
     int64_t o_bs, int64_t o_rs, int64_t o_hs, int64_t do_bs, int64_t do_rs, int64_t do_hs, int64_t lse_bs, int64_t lse_hs,
     RowMap map, int heads, float* __restrict__ lse_log2, float* __restrict__ dpsum, float* __restrict__ dq_accum) {
+  using P = PrePost<D>;
   const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int sub = lane % P::kLanesPerRow;  // 8-column group of the row
+  const int64_t row = (int64_t)blockIdx.x * P::kRowsPerBlock + (threadIdx.x >> 5) * P::kRowsPerWarp + lane / P::kLanesPerRow;
   const int head = blockIdx.y;
-  if (row >= map.rows) return;
-  int batch_coord;
-  int64_t tensor_row;
-  if (!locate_row(map, row, &batch_coord, &tensor_row)) return;
-  constexpr int kPerLane = D / 32;  // 2, 4 or 8 BF16 values
-  const __nv_bfloat16* o_ptr = o + batch_coord * o_bs + tensor_row * o_rs + (int64_t)head * o_hs + lane * kPerLane;
-  const __nv_bfloat16* do_ptr = dout + batch_coord * do_bs + tensor_row * do_rs + (int64_t)head * do_hs + lane * kPerLane;
+  int batch_coord = 0;
+  int64_t tensor_row = 0;
+  const bool active = row < map.rows && locate_row(map, row, &batch_coord, &tensor_row);
   float sum = 0.f;
-  if (lane * kPerLane >= map.head_dim) {
-    // padding columns of a head_dim below the compiled one
-  } else if constexpr (kPerLane == 8) {
-    const uint4 a = *reinterpret_cast<const uint4*>(o_ptr), b = *reinterpret_cast<const uint4*>(do_ptr);
+  if (active && sub * 8 < map.head_dim) {  // columns at and above head_dim are padding of the compiled width
+    const uint4 a = *reinterpret_cast<const uint4*>(o + batch_coord * o_bs + tensor_row * o_rs + (int64_t)head * o_hs + sub * 8);
+    const uint4 b = *reinterpret_cast<const uint4*>(dout + batch_coord * do_bs + tensor_row * do_rs + (int64_t)head * do_hs + sub * 8);
     const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i)
       sum += __uint_as_float(aw[i] << 16) * __uint_as_float(bw[i] << 16) +
              __uint_as_float(aw[i] & 0xffff0000u) * __uint_as_float(bw[i] & 0xffff0000u);
-  } else if constexpr (kPerLane == 4) {
-    const uint2 a = *reinterpret_cast<const uint2*>(o_ptr), b = *reinterpret_cast<const uint2*>(do_ptr);
-    sum = __uint_as_float(a.x << 16) * __uint_as_float(b.x << 16) +
-          __uint_as_float(a.x & 0xffff0000u) * __uint_as_float(b.x & 0xffff0000u) +
-          __uint_as_float(a.y << 16) * __uint_as_float(b.y << 16) +
-          __uint_as_float(a.y & 0xffff0000u) * __uint_as_float(b.y & 0xffff0000u);
-  } else {
-    const uint32_t a = *reinterpret_cast<const uint32_t*>(o_ptr), b = *reinterpret_cast<const uint32_t*>(do_ptr);
-    sum = __uint_as_float(a << 16) * __uint_as_float(b << 16) +
-          __uint_as_float(a & 0xffff0000u) * __uint_as_float(b & 0xffff0000u);
   }
 #pragma unroll
-  for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+  for (int d = P::kLanesPerRow / 2; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+  if (!active) return;
   const int64_t stat = (int64_t)head * map.rows + row;
-  if (lane == 0) {
+  if (sub == 0) {
     const float value = lse[batch_coord * lse_bs + (int64_t)head * lse_hs + tensor_row];
     lse_log2[stat] = value == -INFINITY ? -INFINITY : -value * kLog2e;  // rows without keys: exp2(x + -inf) = 0
     dpsum[stat] = -sum;
   }
-  float* acc = dq_accum + stat * D + lane * kPerLane;
-  if constexpr (kPerLane == 8) {
-    *reinterpret_cast<float4*>(acc) = make_float4(0.f, 0.f, 0.f, 0.f);
-    *reinterpret_cast<float4*>(acc + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
-  } else if constexpr (kPerLane == 4) {
-    *reinterpret_cast<float4*>(acc) = make_float4(0.f, 0.f, 0.f, 0.f);
-  } else {
-    *reinterpret_cast<float2*>(acc) = make_float2(0.f, 0.f);
-  }
+  float4* acc = reinterpret_cast<float4*>(dq_accum + stat * D + sub * 8);
+  acc[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+  acc[1] = make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
-// dq = bf16(scale * dq_accum) for valid rows.
+// dq = bf16(scale * dq_accum) for valid rows (reference zig/flash_bwd_postprocess.zig:139-347).
 template <int D>
 __global__ void __launch_bounds__(256) bwd_postprocess_kernel(const float* __restrict__ dq_accum, RowMap map, float scale,
                                                               __nv_bfloat16* __restrict__ dq, int64_t dq_bs,
                                                               int64_t dq_rs, int64_t dq_hs) {
+  using P = PrePost<D>;
   const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int sub = lane % P::kLanesPerRow;
+  const int64_t row = (int64_t)blockIdx.x * P::kRowsPerBlock + (threadIdx.x >> 5) * P::kRowsPerWarp + lane / P::kLanesPerRow;
   const int head = blockIdx.y;
-  if (row >= map.rows) return;
+  if (row >= map.rows || sub * 8 >= map.head_dim) return;
   int batch_coord;
   int64_t tensor_row;
   if (!locate_row(map, row, &batch_coord, &tensor_row)) return;
-  constexpr int kPerLane = D / 32;
-  const float* acc = dq_accum + ((int64_t)head * map.rows + row) * D + lane * kPerLane;
-  __nv_bfloat16* out = dq + batch_coord * dq_bs + tensor_row * dq_rs + (int64_t)head * dq_hs + lane * kPerLane;
-  if (lane * kPerLane >= map.head_dim) return;
-  if constexpr (kPerLane == 8) {
-    const float4 v = *reinterpret_cast<const float4*>(acc), w = *reinterpret_cast<const float4*>(acc + 4);
-    uint4 packed;
-    packed.x = pack_bf16x2(v.x * scale, v.y * scale);
-    packed.y = pack_bf16x2(v.z * scale, v.w * scale);
-    packed.z = pack_bf16x2(w.x * scale, w.y * scale);
-    packed.w = pack_bf16x2(w.z * scale, w.w * scale);
-    *reinterpret_cast<uint4*>(out) = packed;
-  } else if constexpr (kPerLane == 4) {
-    const float4 v = *reinterpret_cast<const float4*>(acc);
-    uint2 packed;
-    packed.x = pack_bf16x2(v.x * scale, v.y * scale);
-    packed.y = pack_bf16x2(v.z * scale, v.w * scale);
-    *reinterpret_cast<uint2*>(out) = packed;
-  } else {
-    const float2 v = *reinterpret_cast<const float2*>(acc);
-    *reinterpret_cast<uint32_t*>(out) = pack_bf16x2(v.x * scale, v.y * scale);
-  }
+  const float4* acc = reinterpret_cast<const float4*>(dq_accum + ((int64_t)head * map.rows + row) * D + sub * 8);
+  const float4 v = acc[0], w = acc[1];
+  uint4 packed;
+  packed.x = pack_bf16x2(v.x * scale, v.y * scale);
+  packed.y = pack_bf16x2(v.z * scale, v.w * scale);
+  packed.z = pack_bf16x2(w.x * scale, w.y * scale);
+  packed.w = pack_bf16x2(w.z * scale, w.w * scale);
+  *reinterpret_cast<uint4*>(dq + batch_coord * dq_bs + tensor_row * dq_rs + (int64_t)head * dq_hs + sub * 8) = packed;
 }
 
 // ---------------------------------------------------------------------------------------------- host side
@@ -712,7 +691,7 @@ static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
   RowMap map{bp.cu_seqlens_q, bp.batch, bp.seqlen_q, w.rows, bp.head_dim};
   mark(0, stream);
   if (w.rows > 0) {
-    dim3 grid((unsigned)((w.rows + 7) / 8), (unsigned)bp.heads_q);
+    dim3 grid((unsigned)((w.rows + PrePost<D>::kRowsPerBlock - 1) / PrePost<D>::kRowsPerBlock), (unsigned)bp.heads_q);
     bwd_preprocess_kernel<D><<<grid, 256, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(a.out), static_cast<const __nv_bfloat16*>(a.dout), a.softmax_lse,
         packed ? 0 : a.out_stride[0], a.out_stride[1], a.out_stride[2], packed ? 0 : a.dout_stride[0], a.dout_stride[1],
@@ -793,7 +772,7 @@ static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
   mark(2, stream);
 
   if (w.rows > 0) {
-    dim3 post((unsigned)((w.rows + 7) / 8), (unsigned)bp.heads_q);
+    dim3 post((unsigned)((w.rows + PrePost<D>::kRowsPerBlock - 1) / PrePost<D>::kRowsPerBlock), (unsigned)bp.heads_q);
     bwd_postprocess_kernel<D><<<post, 256, 0, stream>>>(dq_accum, map, bp.softmax_scale, static_cast<__nv_bfloat16*>(a.dq),
                                                         packed ? 0 : a.dq_stride[0], a.dq_stride[1], a.dq_stride[2]);
     B200FA_CUDA_CHECK(cudaGetLastError());
