@@ -1,12 +1,14 @@
 """Benchmark of the attention hot path on N GPUs of one node.
 
-    python bench.py --gpus N --steps K --warmup W [--workload c1|c1s|d256s|c4] [--impl reference]
+    python bench.py --gpus N --steps K --warmup W [--workload c1|c1s|d256s|c2|c3|c4] [--impl reference]
 
 One step = one forward + one backward pass of the workload on every rank. Default workload "c1" is the configuration
 the headline metric is quoted on: fixed-length causal GQA, batch 4, seqlen 8192, 32 query / 8 key heads, head_dim
 128, BF16 N(0,1) inputs from a seed. With N > 1 every rank runs its own copy of that batch (independent shards, no
 collective on the data path; scaling "weak"). Workload "c4" is the long-context sharded configuration (batch 16,
-seqlen 32768, 32/4 heads, window (4096, 0)) split evenly by batch over the ranks (scaling "strong").
+seqlen 32768, 32/4 heads, window (4096, 0)) split evenly by batch over the ranks (scaling "strong"). Workloads "c2"
+(packed sequences of 256..8192 tokens, 65536 tokens, window (4096, 0)) and "c3" (inter-sequence visibility bits, shared
+prefixes, head_dim 256) run on one GPU through the packed entry points of the public API.
 
 The JSON line reports whole-job attention TFLOP/s (forward + backward FLOPs of all ranks / max-over-ranks device
 time; FLOPs = 4 * heads_q * head_dim * visible pairs forward, 2.5x that backward), forward and backward TFLOP/s and
@@ -35,6 +37,13 @@ WORKLOADS = {
                 name="one batch entry of c1 (profiling case): batch 1, seqlen 8192, heads 32/8, head_dim 128, causal"),
     "d256s": dict(batch=1, seqlen=8192, heads_q=16, heads_kv=4, head_dim=256, window=(-1, 0), seed=3,
                   name="head_dim 256 profiling case: batch 1, seqlen 8192, heads 16/4, head_dim 256, causal"),
+    "c2": dict(kind="varlen", total=65536, min_len=256, max_len=8192, heads_q=64, heads_kv=8, head_dim=128,
+               window=(4096, 0), seed=2,
+               name="packed (varlen) fwd+bwd: 65536 tokens in sequences of 256..8192, heads 64/8, head_dim 128, window (4096, 0)"),
+    "c3": dict(kind="interseq", groups=8, prefix=2048, continuations=7, continuation_len=512, heads_q=32, heads_kv=8,
+               head_dim=256, seed=3,
+               name="inter-sequence fwd+bwd: 8 groups of a 2048-token prefix and 7 continuations of 512 that see it, "
+                    "heads 32/8, head_dim 256, causal"),
     "c4": dict(batch=16, seqlen=32768, heads_q=32, heads_kv=4, head_dim=128, window=(4096, 0), seed=4,
                name="long-context sharded fwd+bwd: batch 16, seqlen 32768, heads 32/4, head_dim 128, window (4096, 0)"),
 }
@@ -159,6 +168,100 @@ def reference_arm(options, workload):
     print(json.dumps(line))
 
 
+# ------------------------------------------------------------------------------------------------ packed workloads
+def packed_arm(options, workload):
+    """Workloads c2 (varlen) and c3 (inter-sequence) on one GPU through the public API: forward, backward and the
+    backward main kernel by itself, device-timed with the inputs resident in HBM."""
+    import itertools
+
+    import torch
+
+    import zigfa
+    from zigfa._impl import lib
+
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        raise SystemExit("the packed workloads run on one GPU; shard them with zig-flash-attn_b200/sharding.py")
+    torch.cuda.set_device(0)
+    heads_q, heads_kv, d = workload["heads_q"], workload["heads_kv"], workload["head_dim"]
+    warmup, steps = max(options.warmup, 3), options.steps
+    torch.manual_seed(workload["seed"])
+    if workload["kind"] == "varlen":
+        generator = torch.Generator().manual_seed(workload["seed"])
+        lengths = []
+        while sum(lengths) < workload["total"]:
+            lengths.append(int(torch.randint(workload["min_len"], workload["max_len"] + 1, (1,), generator=generator)))
+        lengths[-1] -= sum(lengths) - workload["total"]
+        left = workload["window"][0]
+        pairs = sum(sum(min(i + 1, left + 1) for i in range(n)) for n in lengths)
+    else:
+        lengths = ([workload["prefix"]] + [workload["continuation_len"]] * workload["continuations"]) * workload["groups"]
+        per_group = 1 + workload["continuations"]
+        # visibility bits: bit j of row i (32 per int32 word) = sequence i sees the keys of sequence j
+        words = (len(lengths) + 31) // 32
+        rows = [[0] * words for _ in lengths]
+        for i in range(len(lengths)):
+            for j in {i, i - i % per_group}:  # itself and the prefix of its group
+                rows[i][j // 32] |= 1 << (j % 32)
+        bits = torch.tensor(rows, dtype=torch.int64).to(torch.int32).cuda()
+        p, c = workload["prefix"], workload["continuation_len"]
+        pairs = workload["groups"] * (p * (p + 1) // 2 + workload["continuations"] * (c * (c + 1) // 2 + c * p))
+    total = sum(lengths)
+    cu = torch.tensor([0, *itertools.accumulate(lengths)], dtype=torch.int32, device="cuda")
+    q = torch.randn(total, heads_q, d, device="cuda", dtype=torch.bfloat16).requires_grad_()
+    k, v = (torch.randn(total, heads_kv, d, device="cuda", dtype=torch.bfloat16).requires_grad_() for _ in range(2))
+    dout = torch.randn(total, heads_q, d, device="cuda", dtype=torch.bfloat16)
+    longest = max(lengths)
+
+    def forward():
+        if workload["kind"] == "varlen":
+            return zigfa.flash_attn_varlen_func(q, k, v, cu, cu, longest, longest, window_size=workload["window"])
+        return zigfa.flash_attn_inter_sequence_func(q, k, v, cu, cu, longest, longest, bits, causal=True)
+
+    out = forward()
+
+    def backward():
+        return torch.autograd.grad(out, (q, k, v), dout, retain_graph=True)
+
+    def timed(function, count):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(count):
+            function()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / count
+
+    for _ in range(warmup):
+        forward()
+        backward()
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms_fwd, ms_bwd = timed(forward, steps), timed(backward, steps)
+    clocks = sampler.stop()
+    flops_fwd = 4.0 * heads_q * d * pairs
+    flops_bwd = 2.5 * flops_fwd
+    peaks = measured_peaks()
+    line = {
+        "metric": "attn_fwd_bwd_tflops", "value": (flops_fwd + flops_bwd) / ((ms_fwd + ms_bwd) * 1e-3) / 1e12,
+        "unit": "TFLOP/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": ms_fwd + ms_bwd,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": workload["name"], "sequences": len(lengths), "tokens": total,
+                   "l2": "inputs exceed the 126 MB L2", "flop_convention": "4*Hq*D*visible_pairs fwd, 2.5x bwd"},
+        "fwd_tflops_per_gpu": flops_fwd / (ms_fwd * 1e-3) / 1e12, "bwd_tflops_per_gpu": flops_bwd / (ms_bwd * 1e-3) / 1e12,
+        "tokens_per_s": total / ((ms_fwd + ms_bwd) * 1e-3), "ms_fwd": ms_fwd, "ms_bwd": ms_bwd,
+        "gpu_launches": steps * 6, "e2e": None,
+        # the whole backward op (work list, preprocess, main kernel, postprocess): autograd runs it on its own thread, out
+        # of reach of the per-thread timing hook that isolates the main kernel in the fixed-length workloads
+        "roofline": {"kernel": "backward op (work list + preprocess + dK/dV/dQ main + postprocess)", "bound": "tensor",
+                     "achieved": flops_bwd / (ms_bwd * 1e-3) / 1e12, "peak": peaks["burst"], "unit": "TFLOP/s",
+                     "frac": flops_bwd / (ms_bwd * 1e-3) / 1e12 / peaks["burst"], "traffic": None,
+                     "peak_source": f"{peaks['source']} cuBLAS BF16 burst"},
+        "clocks": clocks, "device_status": lib.library().b200fa_device_status(),
+    }
+    print(json.dumps(line))
+
+
 # ------------------------------------------------------------------------------------------------ GPU arm
 def main():
     parser = argparse.ArgumentParser()
@@ -171,6 +274,10 @@ def main():
     parser.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     options = parser.parse_args()
     workload = WORKLOADS[options.workload]
+    if workload.get("kind"):
+        if options.impl == "reference":
+            raise SystemExit("the reference arm times the fixed-length workloads")
+        return packed_arm(options, workload)
     if options.impl == "reference":
         return reference_arm(options, workload)
 
