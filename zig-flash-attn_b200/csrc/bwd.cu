@@ -12,8 +12,8 @@
 //   dK  += dS^T Q         SS-MMA  -> TMEM [256+D,256+2D)
 //   dQ   = dS K           SS-MMA  -> TMEM [128,128+D) (over dP^T), drained by the reduce warps into shared memory
 //                                    and added into the FP32 dQ accumulator with TMA reduce-add.
-// Warps 0-7 compute P and dS (two groups of four warps, 64 query columns each), warps 8-11 drain dQ, warp 12 issues
-// MMAs, warp 13 issues TMA loads and the asynchronous copies of the per-row statistics.
+// Warps 0-15 compute P and dS (four groups of four warps, 32 query columns each), warps 16-19 drain dQ, warp 20 issues
+// MMAs, warp 21 issues TMA loads and the asynchronous copies of the per-row statistics.
 // Per iteration the MMA warp issues dV, S^T of the next iteration, then dQ before dK (the drain of dQ gates the next
 // dP^T, which uses the same TMEM columns), then dP^T of the next iteration. The CTAs of a fixed-length problem are
 // ordered by bwd_cta_of (bwd_common.cuh); packed problems take their (sequence, key block) from the work list.
@@ -23,6 +23,9 @@
 
 namespace b200fa {
 
+#ifndef B200FA_BWD_GROUPS
+#define B200FA_BWD_GROUPS 4
+#endif
 template <int D>
 struct BwdConfig {
   static constexpr int kTileBytes = 128 * D * 2;
@@ -39,7 +42,18 @@ struct BwdConfig {
   static constexpr int kOffStats = kOffStage + 2 * kStageBytes;  // lse[2][128], dpsum[2][128] floats
   static constexpr int kOffBars = kOffStats + 4 * 512;
   static constexpr int kSmemBytes = kOffBars + 128;
-  static constexpr int kThreads = 512;  // 2 compute warpgroups, 1 dQ-drain warpgroup, 1 warpgroup with the MMA and load warps
+  // Compute warpgroups (P, dS): each thread handles one key row and 128 / kGroups query columns.
+  // Four groups of 32 columns instead of two of 64 halve the latency of the P and dS phases, which sit on the serial
+  // chain of an iteration (989 against 880 TF/s on batch 4, seqlen 8192, heads 32/8, causal).
+  static constexpr int kGroups = B200FA_BWD_GROUPS;
+  static constexpr int kCols = 128 / kGroups;
+  static constexpr int kComputeWarps = 4 * kGroups;
+  // Registers of the compute, drain and MMA/load warpgroups (setmaxnreg). They add up to the launch allocation:
+  // 2 groups: 512 threads x 128 = 2 x 128 x 168 + 128 x 96 + 128 x 80; 4 groups: 768 threads x 80 = 4 x 128 x 88 + 128 x 72 + 128 x 56.
+  static constexpr int kRegsCompute = kGroups == 2 ? 168 : 88, kRegsDrain = kGroups == 2 ? 96 : 72;
+  static constexpr int kRegsMisc = kGroups == 2 ? 80 : 56;
+  static_assert(kGroups == 2 || kGroups == 4, "two or four compute warpgroups");
+  static constexpr int kThreads = 32 * (kComputeWarps + 8);  // + 1 dQ-drain warpgroup, 1 warpgroup with the MMA and load warps
   static constexpr int kTmemS = 0, kTmemDp = 128, kTmemDv = 256, kTmemDk = 256 + D;
 };
 
@@ -105,16 +119,17 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     mbar_init(bar_do_full, 33);
     mbar_init(bar_do_empty, 1);
     mbar_init(bar_s_full, 1);
-    mbar_init(bar_p_full, 256);
+    mbar_init(bar_p_full, 32 * Cfg::kComputeWarps);
     mbar_init(bar_dp_full, 1);
-    mbar_init(bar_ds_full, 256);
+    mbar_init(bar_ds_full, 32 * Cfg::kComputeWarps);
     mbar_init(bar_dq_full, 1);
     mbar_init(bar_dq_empty, 128);
     mbar_init(bar_final, 1);
     mbar_init(bar_ds_empty, 1);
     fence_barrier_init();
   }
-  if (warp == 12) {
+  constexpr int kMmaWarp = Cfg::kComputeWarps + 4, kLoadWarp = Cfg::kComputeWarps + 5;
+  if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -134,10 +149,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   }
   const int iterations = blocks_per_head * group;
 
-  // Register split (setmaxnreg, one site per warpgroup): 2 x 128 x 168 + 128 x 96 + 128 x 80 = 65536.
-  if (warp >= 12) {
-   setmaxnreg_dec<80>();
-   if (warp == 13) {
+  // Register split (setmaxnreg, one site per warpgroup): see BwdConfig.
+  if (warp >= kMmaWarp) {
+   setmaxnreg_dec<Cfg::kRegsMisc>();
+   if (warp == kLoadWarp) {
     // ------------------------------------------------------------------ loads
     if (lane == 0) {
       tma_prefetch_descriptor(&map_q);
@@ -194,7 +209,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         ++it;
       }
     }
-   } else if (warp == 12) {
+   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && iterations > 0) {
       constexpr uint32_t idesc_st = umma_idesc_bf16(128, 128, 0, 0);   // S^T, dP^T
@@ -231,8 +246,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ts(t_dv, t_s + (kk >> 2) * 64 + (kk & 3) * 8, umma_smem_desc(smem_do + kk * 2048, Cfg::kPanelBytes, 1024),
-                  idesc_dv, it > 0 || kk > 0);
+          umma_ts(t_dv, t_s + (Cfg::kGroups == 2 ? (kk >> 2) * 64 + (kk & 3) * 8 : (kk >> 1) * 32 + (kk & 1) * 8),
+                  umma_smem_desc(smem_do + kk * 2048, Cfg::kPanelBytes, 1024), idesc_dv, it > 0 || kk > 0);
         tc_commit(bar_do_empty);
         trace_event(wctx, traced_cta && it < 10, 0, trace_n, 100 + it);  // dV issued
         // S^T of the next iteration
@@ -281,12 +296,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       if (ok) tc_commit(bar_final);
     }
    }
-  } else if (warp < 8) {
-    setmaxnreg_inc<168>();
+  } else if (warp < Cfg::kComputeWarps) {
+    setmaxnreg_inc<Cfg::kRegsCompute>();
+    constexpr int C = Cfg::kCols;
     // ------------------------------------------------------------------ P and dS (thread = key row)
     const int wg = warp >> 2;
     const int r = (warp & 3) * 32 + lane;
-    const int cb = wg * 64;  // first query column of this group
+    const int cb = wg * C;  // first query column of this group
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_s = tmem_base + lane_addr + Cfg::kTmemS, t_dp = tmem_base + lane_addr + Cfg::kTmemDp;
     const int c = n0 + r;  // key column within its sequence
@@ -294,7 +310,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     int left, right;
     window_of(pr, seq, &left, &right);
     const int off = s.lk - s.lq;
-    const uint32_t ds_row = smem_ds + wg * Cfg::kPanelBytes + r * 128;
+    const uint32_t ds_row = smem_ds + (cb >> 6) * Cfg::kPanelBytes + r * 128;  // panel of 64 query columns
+    const int ds_chunk0 = (cb & 63) >> 3;                                      // first 16-byte chunk within the row
     int it = 0;
     bool ok = true;
     for (int g = 0; ok && g < group; ++g) {
@@ -309,19 +326,19 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           if (left >= 0) qhi = imin(qhi, c - off + left + 1 - qb.col0);
         }
         if (!key_valid) qhi = 0;
-        const bool masked = __any_sync(0xffffffffu, qlo > cb || qhi < cb + 64);
+        const bool masked = __any_sync(0xffffffffu, qlo > cb || qhi < cb + C);
         // ---- P^T (kept in FP32 registers for dS, stored to TMEM as BF16 for the dV MMA)
         if (!mbar_wait_traced(bar_s_full, it & 1, wctx, kWaitBwdCompute, 7, true)) { ok = false; break; }
         tc_fence_after();
         const long long t_p = trace_clock(wctx);
         trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 500 + it);  // S ready
-        float pf[64];
+        float pf[C];
         tmem_ld32(t_s + cb, reinterpret_cast<uint32_t*>(pf));
-        tmem_ld32(t_s + cb + 32, reinterpret_cast<uint32_t*>(pf) + 32);
+        if constexpr (C == 64) tmem_ld32(t_s + cb + 32, reinterpret_cast<uint32_t*>(pf) + 32);
         tc_wait_ld();
         const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
+        for (int j = 0; j < C / 4; ++j) {
           const float4 l4 = ld_shared_f4(smem_lse + st * 512 + (cb + 4 * j) * 4);  // -lse * log2(e)
           const float2 x01 = __ffma2_rn(make_float2(pf[4 * j + 0], pf[4 * j + 1]), scale2, make_float2(l4.x, l4.y));
           const float2 x23 = __ffma2_rn(make_float2(pf[4 * j + 2], pf[4 * j + 3]), scale2, make_float2(l4.z, l4.w));
@@ -338,9 +355,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           pf[4 * j + 2] = p2;
           pf[4 * j + 3] = p3;
         }
-        // P^T of a group goes over the first 32 columns of the group's own S^T columns.
+        // P^T of a group goes over the first half of the group's own S^T columns.
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int h = 0; h < C / 32; ++h) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(pf[32 * h + 2 * i], pf[32 * h + 2 * i + 1]);
@@ -359,7 +376,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         const long long t_ds = trace_clock(wctx);
         trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 700 + it);  // dP ready
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int h = 0; h < C / 32; ++h) {
           float dp[32];
           tmem_ld32(t_dp + cb + 32 * h, reinterpret_cast<uint32_t*>(dp));
           tc_wait_ld();
@@ -385,7 +402,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
               packed[2 * e] = pack_bf16x2(s0, s1);
               packed[2 * e + 1] = pack_bf16x2(s2, s3);
             }
-            st_shared_v4(ds_row + (((4 * h + j) ^ (r & 7)) << 4), packed[0], packed[1], packed[2], packed[3]);
+            st_shared_v4(ds_row + (((ds_chunk0 + 4 * h + j) ^ (r & 7)) << 4), packed[0], packed[1], packed[2], packed[3]);
           }
         }
         tc_fence_before();
@@ -402,15 +419,20 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       if (have) ok = mbar_wait_warp(bar_final, 0, wctx, kWaitEpilogue);
       if (ok) {
         tc_fence_after();
-        __nv_bfloat16* out = wg == 0 ? p.dv : p.dk;
-        const int64_t bs = wg == 0 ? p.dv_batch_stride : p.dk_batch_stride;
-        const int64_t rs = wg == 0 ? p.dv_row_stride : p.dk_row_stride;
-        const int64_t hs = wg == 0 ? p.dv_head_stride : p.dk_head_stride;
-        const float mul = wg == 0 ? 1.f : p.scale;
-        const uint32_t t_acc = tmem_base + lane_addr + (wg == 0 ? Cfg::kTmemDv : Cfg::kTmemDk);
+        // The first half of the groups writes dV, the second half dK * scale; a group writes D / kParts columns.
+        constexpr int kParts = Cfg::kGroups / 2;
+        const bool is_dv = wg < kParts;
+        const int part = is_dv ? wg : wg - kParts;
+        __nv_bfloat16* out = is_dv ? p.dv : p.dk;
+        const int64_t bs = is_dv ? p.dv_batch_stride : p.dk_batch_stride;
+        const int64_t rs = is_dv ? p.dv_row_stride : p.dk_row_stride;
+        const int64_t hs = is_dv ? p.dv_head_stride : p.dk_head_stride;
+        const float mul = is_dv ? 1.f : p.scale;
+        const uint32_t t_acc = tmem_base + lane_addr + (is_dv ? Cfg::kTmemDv : Cfg::kTmemDk);
         uint4* dst = reinterpret_cast<uint4*>(out + s.batch_coord * bs + (int64_t)(s.k0 + c) * rs + (int64_t)kv_head * hs);
 #pragma unroll
-        for (int ch = 0; ch < D / 32; ++ch) {
+        for (int ch0 = 0; ch0 < D / 32 / kParts; ++ch0) {
+          const int ch = part * (D / 32 / kParts) + ch0;
           uint32_t acc[32];
           if (have) {
             tmem_ld32(t_acc + 32 * ch, acc);
@@ -435,12 +457,12 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       }
     }
   } else {
-    setmaxnreg_dec<96>();
-    // ------------------------------------------------------------------ dQ drain (warps 8-11, thread = query row)
+    setmaxnreg_dec<Cfg::kRegsDrain>();
+    // ------------------------------------------------------------------ dQ drain (one warpgroup, thread = query row)
     const int r = (warp & 3) * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_dq = tmem_base + lane_addr + Cfg::kTmemDp;
-    const bool leader = threadIdx.x == 8 * 32;
+    const bool leader = threadIdx.x == Cfg::kComputeWarps * 32;
     int it = 0;
     uint32_t chunks = 0;
     bool ok = true;
@@ -461,7 +483,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           if (ch == D / 32 - 1) {
             tc_fence_before();
             mbar_arrive(bar_dq_empty);
-            trace_event(wctx, traced_cta && threadIdx.x == 256 && it < 10, 2, trace_n, 900 + it);  // dQ drained
+            trace_event(wctx, traced_cta && leader && it < 10, 2, trace_n, 900 + it);  // dQ drained
           }
           const uint32_t stage = smem_stage + (chunks & 1) * Cfg::kStageBytes;
           if (leader) bulk_wait_group_read<1>();  // the copy that read this buffer two chunks ago is done with it
@@ -491,7 +513,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 12) tmem_dealloc(tmem_base, 512);
+  if (warp == kMmaWarp) tmem_dealloc(tmem_base, 512);
   if (kTraceBuild && threadIdx.x == 0) {
     trace_add(wctx, 11, trace_clock(wctx) - trace_start);
     trace_add(wctx, 12, iterations);
