@@ -17,15 +17,21 @@
 //                           dQ accumulator with TMA reduce-add.
 // Shared memory holds K and V of the block (64 KB each), one Q and one dO tile (32 KB each, single-buffered: there
 // is no room for a second stage), the dS tile and two 8 KB staging buffers.
-// Warps 0-7 compute P and dS (two groups, 32 query columns each), warps 8-11 drain dQ, warp 12 issues MMAs, warp 13
+// Warps 0-15 compute P and dS (four groups, 16 query columns each), warps 16-19 drain dQ, warp 20 issues MMAs, warp 21
 // issues the loads.
 #include "bwd_common.cuh"
 
 namespace b200fa {
 namespace bd256 {
 
-constexpr int kThreads = 512;
 constexpr int kSubM = 64;                   // query rows per iteration
+constexpr int kGroups = 4;                   // compute warpgroups: a thread handles one key row and 64 / kGroups query columns
+constexpr int kCols = kSubM / kGroups;
+constexpr int kComputeWarps = 4 * kGroups;
+constexpr int kMmaWarp = kComputeWarps + 4, kLoadWarp = kComputeWarps + 5;
+constexpr int kThreads = 32 * (kComputeWarps + 8);
+// registers per thread of the compute, drain and MMA/load warpgroups: 4 x 128 x 88 + 128 x 72 + 128 x 56 = 768 x 80
+constexpr int kRegsCompute = 88, kRegsDrain = 72, kRegsMisc = 56;
 constexpr int kKvPanel = 128 * 128;         // 128 key rows x 64 columns BF16
 constexpr int kKvBytes = 4 * kKvPanel;      // 64 KB
 constexpr int kQPanel = kSubM * 128;        // 64 query rows x 64 columns BF16
@@ -128,16 +134,16 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     mbar_init(bar_do_full, 33);
     mbar_init(bar_do_empty, 1);
     mbar_init(bar_s_full, 1);
-    mbar_init(bar_p_full, 256);
+    mbar_init(bar_p_full, 32 * kComputeWarps);
     mbar_init(bar_dp_full, 1);
-    mbar_init(bar_ds_full, 256);
+    mbar_init(bar_ds_full, 32 * kComputeWarps);
     mbar_init(bar_ds_empty, 1);
     mbar_init(bar_dq_full, 1);
     mbar_init(bar_dq_empty, 128);
     mbar_init(bar_final, 1);
     fence_barrier_init();
   }
-  if (warp == 12) {
+  if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -156,10 +162,10 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   }
   const int iterations = blocks_per_head * group;
 
-  // Register split (setmaxnreg, one site per warpgroup): 2 x 128 x 168 + 128 x 96 + 128 x 80 = 65536.
-  if (warp >= 12) {
-   setmaxnreg_dec<80>();
-   if (warp == 13) {
+  // Register split (setmaxnreg, one site per warpgroup): see kRegsCompute.
+  if (warp >= kMmaWarp) {
+   setmaxnreg_dec<kRegsMisc>();
+   if (warp == kLoadWarp) {
     // ------------------------------------------------------------------ loads
     if (lane == 0) {
       tma_prefetch_descriptor(&map_q);
@@ -212,7 +218,7 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         ++it;
       }
     }
-   } else if (warp == 12) {
+   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && iterations > 0) {
       constexpr uint32_t idesc_st = umma_idesc_bf16(128, kSubM, 0, 0);  // S^T, dP^T: both operands K-major
@@ -250,7 +256,7 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ts(t_dv, t_s + (kk >> 1) * 32 + (kk & 1) * 8, umma_smem_desc(do_half + kk * 2048, kQPanel, 1024), idesc_dv,
+          umma_ts(t_dv, t_s + kk * kCols, umma_smem_desc(do_half + kk * 2048, kQPanel, 1024), idesc_dv,
                   it > 0 || kk > 0);
         tc_commit(bar_do_empty);
         // dK_h += dS^T Q_h ; dQ_h^T = K_h^T dS^T
@@ -271,12 +277,12 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if (ok) tc_commit(bar_final);
     }
    }
-  } else if (warp < 8) {
-    setmaxnreg_inc<168>();
+  } else if (warp < kComputeWarps) {
+    setmaxnreg_inc<kRegsCompute>();
     // ------------------------------------------------------------------ P and dS (thread = key row)
     const int wg = warp >> 2;
     const int r = (warp & 3) * 32 + lane;
-    const int cb = wg * 32;  // first query column of this group
+    const int cb = wg * kCols;  // first query column of this group (16 columns = one k-step of the dV MMA)
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_s = tmem_base + lane_addr + kTmemS, t_dp = tmem_base + lane_addr + kTmemDp;
     const int c = n0 + r;  // key column within its sequence
@@ -299,16 +305,16 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           if (left >= 0) qhi = imin(qhi, c - off + left + 1 - qb.col0);
         }
         if (!key_valid) qhi = 0;
-        const bool masked = __any_sync(0xffffffffu, qlo > cb || qhi < cb + 32);
+        const bool masked = __any_sync(0xffffffffu, qlo > cb || qhi < cb + kCols);
         // ---- P^T (kept in FP32 registers for dS, stored to TMEM as BF16 for the dV MMA)
         if (!mbar_wait(bar_s_full, it & 1, wctx, kWaitBwdCompute)) { ok = false; break; }
         tc_fence_after();
-        float pf[32];
-        tmem_ld32(t_s + cb, reinterpret_cast<uint32_t*>(pf));
+        float pf[kCols];
+        tmem_ld16(t_s + cb, reinterpret_cast<uint32_t*>(pf));
         tc_wait_ld();
         const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < kCols / 4; ++j) {
           const float4 l4 = ld_shared_f4(smem_lse + st * 256 + (cb + 4 * j) * 4);  // -lse * log2(e)
           const float2 x01 = __ffma2_rn(make_float2(pf[4 * j + 0], pf[4 * j + 1]), scale2, make_float2(l4.x, l4.y));
           const float2 x23 = __ffma2_rn(make_float2(pf[4 * j + 2], pf[4 * j + 3]), scale2, make_float2(l4.z, l4.w));
@@ -325,11 +331,11 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           pf[4 * j + 2] = p2;
           pf[4 * j + 3] = p3;
         }
-        {  // P^T of a group goes over the first 16 columns of the group's own S^T columns
-          uint32_t pk[16];
+        {  // P^T of a group goes over the first half of the group's own S^T columns
+          uint32_t pk[kCols / 2];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(pf[2 * i], pf[2 * i + 1]);
-          tmem_st16(t_s + cb, pk);
+          for (int i = 0; i < kCols / 2; ++i) pk[i] = pack_bf16x2(pf[2 * i], pf[2 * i + 1]);
+          tmem_st8(t_s + cb, pk);
         }
         tc_wait_st();
         tc_fence_before();
@@ -339,11 +345,11 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         // The dS tile of the previous iteration must have been consumed by its dK and dQ MMAs.
         if (it > 0 && !mbar_wait(bar_ds_empty, (it - 1) & 1, wctx, kWaitBwdCompute)) { ok = false; break; }
         tc_fence_after();
-        float dp[32];
-        tmem_ld32(t_dp + cb, reinterpret_cast<uint32_t*>(dp));
+        float dp[kCols];
+        tmem_ld16(t_dp + cb, reinterpret_cast<uint32_t*>(dp));
         tc_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {  // 8 queries = one 16-byte chunk
+        for (int j = 0; j < kCols / 8; ++j) {  // 8 queries = one 16-byte chunk
           uint32_t packed[4];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
@@ -364,7 +370,7 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             packed[2 * e] = pack_bf16x2(s0, s1);
             packed[2 * e + 1] = pack_bf16x2(s2, s3);
           }
-          st_shared_v4(ds_row + (((4 * wg + j) ^ (r & 7)) << 4), packed[0], packed[1], packed[2], packed[3]);
+          st_shared_v4(ds_row + ((((cb >> 3) + j) ^ (r & 7)) << 4), packed[0], packed[1], packed[2], packed[3]);
         }
         tc_fence_before();
         fence_proxy_async_smem();
@@ -372,21 +378,25 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         ++it;
       }
     }
-    // ---- epilogue: group 0 writes its half of dV, group 1 its half of dK * scale
+    // ---- epilogue
     if (ok) {
       const bool have = iterations > 0;
       if (have) ok = mbar_wait_warp(bar_final, 0, wctx, kWaitEpilogue);
       if (ok) {
         tc_fence_after();
-        __nv_bfloat16* out = wg == 0 ? p.dv : p.dk;
-        const int64_t bs = wg == 0 ? p.dv_batch_stride : p.dk_batch_stride;
-        const int64_t rs = wg == 0 ? p.dv_row_stride : p.dk_row_stride;
-        const int64_t hs = wg == 0 ? p.dv_head_stride : p.dk_head_stride;
-        const float mul = wg == 0 ? 1.f : p.scale;
-        const uint32_t t_acc = tmem_base + lane_addr + (wg == 0 ? kTmemDv : kTmemDk);
+        // groups 0 and 1 write the two 64-column halves of dV, groups 2 and 3 those of dK * scale
+        const bool is_dv = wg < kGroups / 2;
+        const int part = wg & 1;
+        __nv_bfloat16* out = is_dv ? p.dv : p.dk;
+        const int64_t bs = is_dv ? p.dv_batch_stride : p.dk_batch_stride;
+        const int64_t rs = is_dv ? p.dv_row_stride : p.dk_row_stride;
+        const int64_t hs = is_dv ? p.dv_head_stride : p.dk_head_stride;
+        const float mul = is_dv ? 1.f : p.scale;
+        const uint32_t t_acc = tmem_base + lane_addr + (is_dv ? kTmemDv : kTmemDk);
         uint4* dst = reinterpret_cast<uint4*>(out + s.batch_coord * bs + (int64_t)(s.k0 + c) * rs + (int64_t)kv_head * hs + dh * 128);
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
+        for (int ch0 = 0; ch0 < 2; ++ch0) {
+          const int ch = 2 * part + ch0;
           uint32_t acc[32];
           if (have) {
             tmem_ld32(t_acc + 32 * ch, acc);
@@ -411,12 +421,12 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
     }
   } else {
-    setmaxnreg_dec<96>();
-    // ------------------------------------------------------------------ dQ drain (warps 8-11, thread = head-dim column)
+    setmaxnreg_dec<kRegsDrain>();
+    // ------------------------------------------------------------------ dQ drain (one warpgroup, thread = head-dim column)
     const int d = (warp & 3) * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_dq = tmem_base + lane_addr + kTmemDp;
-    const bool leader = threadIdx.x == 8 * 32;
+    const bool leader = threadIdx.x == kComputeWarps * 32;
     int it = 0;
     uint32_t chunks = 0;
     bool ok = true;
@@ -465,7 +475,7 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 12) tmem_dealloc(tmem_base, 512);
+  if (warp == kMmaWarp) tmem_dealloc(tmem_base, 512);
 }
 
 }  // namespace bd256
