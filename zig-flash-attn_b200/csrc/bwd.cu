@@ -12,8 +12,9 @@
 //   dK  += dS^T Q         SS-MMA  -> TMEM [256+D,256+2D)
 //   dQ   = dS K           SS-MMA  -> TMEM [128,128+D) (over dP^T), drained by the reduce warps into shared memory
 //                                    and added into the FP32 dQ accumulator with TMA reduce-add.
-// Warps 0-15 compute P and dS (four groups of four warps, 32 query columns each), warps 16-19 drain dQ, warp 20 issues
-// MMAs, warp 21 issues TMA loads and the asynchronous copies of the per-row statistics.
+// Warps 0-15 compute P and dS (four groups of four warps, 32 query columns each), warps 16-23 drain dQ (two groups, half
+// of the columns each), warp 24 issues MMAs, warp 25 issues TMA loads and the asynchronous copies of the per-row
+// statistics.
 // Per iteration the MMA warp issues dV, S^T of the next iteration, then dQ before dK (the drain of dQ gates the next
 // dP^T, which uses the same TMEM columns), then dP^T of the next iteration. The CTAs of a fixed-length problem are
 // ordered by bwd_cta_of (bwd_common.cuh); packed problems take their (sequence, key block) from the work list.
@@ -25,6 +26,9 @@ namespace b200fa {
 
 #ifndef B200FA_BWD_GROUPS
 #define B200FA_BWD_GROUPS 4
+#endif
+#ifndef B200FA_BWD_DRAINS
+#define B200FA_BWD_DRAINS 2
 #endif
 template <int D>
 struct BwdConfig {
@@ -49,11 +53,18 @@ struct BwdConfig {
   static constexpr int kCols = 128 / kGroups;
   static constexpr int kComputeWarps = 4 * kGroups;
   // Registers of the compute, drain and MMA/load warpgroups (setmaxnreg). They add up to the launch allocation:
-  // 2 groups: 512 threads x 128 = 2 x 128 x 168 + 128 x 96 + 128 x 80; 4 groups: 768 threads x 80 = 4 x 128 x 88 + 128 x 72 + 128 x 56.
-  static constexpr int kRegsCompute = kGroups == 2 ? 168 : 88, kRegsDrain = kGroups == 2 ? 96 : 72;
-  static constexpr int kRegsMisc = kGroups == 2 ? 80 : 56;
+  // 2 groups: 512 threads x 128 = 2 x 128 x 168 + 128 x 96 + 128 x 80; 4 groups and 1 drain group: 768 threads x 80 =
+  // 4 x 128 x 88 + 128 x 72 + 128 x 56; 4 groups and 2 drain groups: 896 threads x 72 = 4 x 128 x 88 + 2 x 128 x 56 + 128 x 40.
+  // dQ-drain warpgroups, each takes D / kDrains columns: with two the accumulator is released after one staging step
+  // instead of three (1017 against 969 TF/s).
+  static constexpr int kDrains = kGroups == 4 ? B200FA_BWD_DRAINS : 1;
+  static constexpr int kRegsCompute = kGroups == 2 ? 168 : 88, kRegsDrain = kGroups == 2 ? 96 : (kDrains == 2 ? 56 : 72);
+  static constexpr int kRegsMisc = kGroups == 2 ? 80 : (kDrains == 2 ? 40 : 56);
+  static_assert(32 * (4 * kGroups + 4 * kDrains + 4) * (kGroups == 2 ? 128 : kDrains == 2 ? 72 : 80) ==
+                    128 * (kGroups * kRegsCompute + kDrains * kRegsDrain + kRegsMisc),
+                "the setmaxnreg budgets must add up to the launch allocation");
   static_assert(kGroups == 2 || kGroups == 4, "two or four compute warpgroups");
-  static constexpr int kThreads = 32 * (kComputeWarps + 8);  // + 1 dQ-drain warpgroup, 1 warpgroup with the MMA and load warps
+  static constexpr int kThreads = 32 * (kComputeWarps + 4 * kDrains + 4);  // + 1 dQ-drain warpgroup, 1 warpgroup with the MMA and load warps
   static constexpr int kTmemS = 0, kTmemDp = 128, kTmemDv = 256, kTmemDk = 256 + D;
 };
 
@@ -123,12 +134,12 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     mbar_init(bar_dp_full, 1);
     mbar_init(bar_ds_full, 32 * Cfg::kComputeWarps);
     mbar_init(bar_dq_full, 1);
-    mbar_init(bar_dq_empty, 128);
+    mbar_init(bar_dq_empty, 128 * Cfg::kDrains);
     mbar_init(bar_final, 1);
     mbar_init(bar_ds_empty, 1);
     fence_barrier_init();
   }
-  constexpr int kMmaWarp = Cfg::kComputeWarps + 4, kLoadWarp = Cfg::kComputeWarps + 5;
+  constexpr int kMmaWarp = Cfg::kComputeWarps + 4 * Cfg::kDrains, kLoadWarp = kMmaWarp + 1;
   if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
@@ -462,7 +473,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     const int r = (warp & 3) * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_dq = tmem_base + lane_addr + Cfg::kTmemDp;
-    const bool leader = threadIdx.x == Cfg::kComputeWarps * 32;
+    // Drain warpgroup `dg` takes the columns [dg * D / kDrains, (dg + 1) * D / kDrains) of dQ; with two groups each has one
+    // staging buffer of its own and the accumulator is released after one staging step instead of three.
+    const int dg = (warp - Cfg::kComputeWarps) >> 2;
+    const bool leader = (threadIdx.x & 127) == 0;
+    constexpr int kChunks = D / 32 / Cfg::kDrains;
     int it = 0;
     uint32_t chunks = 0;
     bool ok = true;
@@ -476,24 +491,27 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         if (!mbar_wait_traced(bar_dq_full, it & 1, wctx, kWaitBwdReduce, 10, true)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
-        for (int ch = 0; ch < D / 32; ++ch) {
+        for (int c0 = 0; c0 < kChunks; ++c0) {
+          const int ch = dg * kChunks + c0;
           uint32_t acc[32];
           tmem_ld32(t_dq + 32 * ch, acc);
           tc_wait_ld();
-          if (ch == D / 32 - 1) {
+          if (c0 == kChunks - 1) {
             tc_fence_before();
             mbar_arrive(bar_dq_empty);
-            trace_event(wctx, traced_cta && leader && it < 10, 2, trace_n, 900 + it);  // dQ drained
+            trace_event(wctx, traced_cta && leader && dg == 0 && it < 10, 2, trace_n, 900 + it);  // dQ drained
           }
-          const uint32_t stage = smem_stage + (chunks & 1) * Cfg::kStageBytes;
-          if (leader) bulk_wait_group_read<1>();  // the copy that read this buffer two chunks ago is done with it
-          named_barrier_sync(1, 128);
+          const uint32_t stage = smem_stage + (Cfg::kDrains == 2 ? dg : (chunks & 1)) * Cfg::kStageBytes;
+          if (leader) {  // the copy that last read this buffer is done with it
+            if (Cfg::kDrains == 2) bulk_wait_group_read<0>(); else bulk_wait_group_read<1>();
+          }
+          named_barrier_sync(1 + dg, 128);
           const uint32_t row_addr = stage + r * 128;
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             st_shared_v4(row_addr + ((j ^ (r & 7)) << 4), acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
           fence_proxy_async_smem();
-          named_barrier_sync(1, 128);
+          named_barrier_sync(1 + dg, 128);
           if (leader) {
             tma_reduce_add_4d(&map_dq, stage, 32 * ch, head, row0, 0);
             bulk_commit_group();
