@@ -57,7 +57,7 @@ struct BwdConfig {
   // 4 x 128 x 88 + 128 x 72 + 128 x 56; 4 groups and 2 drain groups: 896 threads x 72 = 4 x 128 x 88 + 2 x 128 x 56 + 128 x 40.
   // dQ-drain warpgroups, each takes D / kDrains columns: with two the accumulator is released after one staging step
   // instead of three (1017 against 969 TF/s).
-  static constexpr int kDrains = kGroups == 4 ? B200FA_BWD_DRAINS : 1;
+  static constexpr int kDrains = (kGroups == 4 && D == 128) ? B200FA_BWD_DRAINS : 1;  // head_dim 64 has two chunks only: 645 (one group) against 601 TF/s
   static constexpr int kRegsCompute = kGroups == 2 ? 168 : 88, kRegsDrain = kGroups == 2 ? 96 : (kDrains == 2 ? 56 : 72);
   static constexpr int kRegsMisc = kGroups == 2 ? 80 : (kDrains == 2 ? 40 : 56);
   static_assert(32 * (4 * kGroups + 4 * kDrains + 4) * (kGroups == 2 ? 128 : kDrains == 2 ? 72 : 80) ==
