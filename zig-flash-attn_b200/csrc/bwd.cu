@@ -761,7 +761,7 @@ static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
   if (!p.status) return B200FA_ERR_CUDA;
   p.trace = trace_buffer();
 
-  constexpr int kBwdSection = 8;  // (batch entry, head slot) pairs per section of the launch order
+  constexpr int kBwdSection = 4;  // (batch entry, head slot) pairs per section of the launch order
   constexpr unsigned kHeadSplit = D == 256 ? 2 : 1;  // the 256-column kernel runs one CTA per half of the head dimension
   dim3 grid;
   bool run_main = !no_keys;
