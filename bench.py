@@ -470,8 +470,8 @@ def main():
                          "achieved": flops_bwd / (ms_main * 1e-3) / 1e12, "peak": peaks["burst"], "unit": "TFLOP/s",
                          "frac": flops_bwd / (ms_main * 1e-3) / 1e12 / peaks["burst"],
                          # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture on one batch entry of this
-                         # workload (profiles/bwd_kernel_d128_c1s.md: 898.3 MB), scaled by the batch entries per launch
-                         "traffic": 898.3e6 * batch if options.workload in ("c1", "c1s") else None,
+                         # workload (profiles/bwd_kernel_d128_c1s.md: 519.9 MB), scaled by the batch entries per launch
+                         "traffic": 519.9e6 * batch if options.workload in ("c1", "c1s") else None,
                          "peak_source": f"{peaks['source']} cuBLAS BF16 burst", "sustained_peak": peaks["sustained"]},
             "roofline_fwd": {"kernel": "fwd_d256_kernel" if d > 128 else f"fwd_kernel<{64 if d <= 64 else 128}>", "bound": "tensor", "achieved": flops_fwd / (ms_fwd * 1e-3) / 1e12,
                              "peak": peaks["burst"], "unit": "TFLOP/s",
