@@ -9,14 +9,18 @@
 //
 // Per iteration a CTA takes 64 query rows of one head (a 128-row block of the QueryCursor in two halves):
 //   S^T  = K Q^T            SS-MMA 128x64x256   -> TMEM [0,64)        P^T  = exp2(S^T c - lse)  (BF16, over S^T)
-//   dP^T = V dO^T           SS-MMA 128x64x256   -> TMEM [64,128)      dS^T = P^T o (dP^T - D)   (BF16, shared memory)
+//   dP^T = V dO^T           TS-MMA 128x64x256   -> TMEM [64,128)      dS^T = P^T o (dP^T - D)   (BF16, shared memory)
 //   dV_h += P^T dO_h        TS-MMA 128x128x64   -> TMEM [128,256)
 //   dK_h += dS^T Q_h        SS-MMA 128x128x64   -> TMEM [256,384)
 //   dQ_h^T = K_h^T dS^T     SS-MMA 128x64x128   -> TMEM [64,128) (over dP^T): head-dim columns on the lanes, queries on
 //                           the columns; the drain warps transpose it through shared memory and add it into the FP32
 //                           dQ accumulator with TMA reduce-add.
-// Shared memory holds K and V of the block (64 KB each), one Q and one dO tile (32 KB each, single-buffered: there
-// is no room for a second stage), the dS tile and two 8 KB staging buffers.
+// V of the key block lives in TMEM (128 columns of BF16 pairs, copied there once): dP^T = V dO^T then reads only dO from
+// shared memory (a 128 x 64 x 16 MMA with both operands in shared memory needs 6 KB per 32 tensor cycles, more than
+// the SM delivers), and the 64 KB that V would take hold a second Q / dO stage, so the loads of the next iteration
+// and its S^T MMA overlap the current one.
+// Shared memory: K of the block (64 KB), two stages of a Q and a dO tile (32 KB each), the dS tile, two 8 KB staging
+// buffers.
 // Warps 0-15 compute P and dS (four groups, 16 query columns each), warps 16-19 drain dQ, warp 20 issues MMAs, warp 21
 // issues the loads.
 #include "bwd_common.cuh"
@@ -40,15 +44,15 @@ constexpr int kDsBytes = 128 * 128;         // 128 keys x 64 queries BF16
 constexpr int kStageRows = 16;              // query rows per staging buffer
 constexpr int kStageBytes = kStageRows * 128 * 4;
 constexpr int kOffK = 0;
-constexpr int kOffV = kOffK + kKvBytes;
-constexpr int kOffQ = kOffV + kKvBytes;
-constexpr int kOffDo = kOffQ + kQBytes;
-constexpr int kOffDs = kOffDo + kQBytes;
+constexpr int kOffQ = kOffK + kKvBytes;     // two stages of (Q tile, dO tile): Q0 dO0 Q1 dO1
+constexpr int kStageStride = 2 * kQBytes;
+constexpr int kOffVTemp = kOffQ + kStageStride;  // V lands in the second stage before it moves to TMEM
+constexpr int kOffDs = kOffQ + 2 * kStageStride;
 constexpr int kOffStage = kOffDs + kDsBytes;
 constexpr int kOffStats = kOffStage + 2 * kStageBytes;  // lse[2][64], dpsum[2][64] floats
 constexpr int kOffBars = kOffStats + 4 * 256;
-constexpr int kSmemBytes = kOffBars + 128;
-constexpr int kTmemS = 0, kTmemDp = 64, kTmemDv = 128, kTmemDk = 256;
+constexpr int kSmemBytes = kOffBars + 192;
+constexpr int kTmemS = 0, kTmemDp = 64, kTmemDv = 128, kTmemDk = 256, kTmemV = 384;
 static_assert(kSmemBytes <= 232448, "shared memory of the head_dim 256 backward kernel exceeds the per-CTA limit");
 
 // Yields the 128-row query blocks of a QueryCursor as 64-row halves (a half past the end of its run is skipped).
@@ -110,15 +114,16 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     if (threadIdx.x == 0) atomicCAS(p.status, 0, (kWaitBwdLoad << 16) | 0xffff);
     return;
   }
-  const uint32_t smem_k = base + kOffK, smem_v = base + kOffV, smem_q = base + kOffQ, smem_do = base + kOffDo;
+  const uint32_t smem_k = base + kOffK, smem_v = base + kOffVTemp, smem_q = base + kOffQ, smem_do = base + kOffQ + kQBytes;
   const uint32_t smem_ds = base + kOffDs, smem_stage = base + kOffStage;
   const uint32_t smem_lse = base + kOffStats, smem_dpsum = smem_lse + 512;
   const uint32_t bars = base + kOffBars;
-  const uint32_t bar_kv_full = bars, bar_q_full = bars + 8, bar_q_empty = bars + 16, bar_do_full = bars + 24;
-  const uint32_t bar_do_empty = bars + 32, bar_s_full = bars + 40, bar_p_full = bars + 48, bar_dp_full = bars + 56;
-  const uint32_t bar_ds_full = bars + 64, bar_ds_empty = bars + 72, bar_dq_full = bars + 80, bar_dq_empty = bars + 88;
-  const uint32_t bar_final = bars + 96;
-  const uint32_t tmem_slot = bars + 104, abort_slot = bars + 108;
+  const uint32_t bar_kv_full = bars, bar_s_full = bars + 8, bar_p_full = bars + 16, bar_dp_full = bars + 24;
+  const uint32_t bar_ds_full = bars + 32, bar_ds_empty = bars + 40, bar_dq_full = bars + 48, bar_dq_empty = bars + 56;
+  const uint32_t bar_final = bars + 64, bar_v_ready = bars + 72;
+  const uint32_t bar_q_full = bars + 80 /*[2]*/, bar_q_empty = bars + 96 /*[2]*/, bar_do_full = bars + 112 /*[2]*/;
+  const uint32_t bar_do_empty = bars + 128 /*[2]*/;
+  const uint32_t tmem_slot = bars + 144, abort_slot = bars + 148;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + (abort_slot - base));
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - base));
   const WaitCtx wctx{abort_flag, p.status, nullptr};
@@ -129,10 +134,13 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(bar_kv_full, 1);
-    mbar_init(bar_q_full, 33);
-    mbar_init(bar_q_empty, 1);
-    mbar_init(bar_do_full, 33);
-    mbar_init(bar_do_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_q_full + 8 * i, 33);
+      mbar_init(bar_q_empty + 8 * i, 1);
+      mbar_init(bar_do_full + 8 * i, 1);
+      mbar_init(bar_do_empty + 8 * i, 1);
+    }
+    mbar_init(bar_v_ready, 32 * kComputeWarps);
     mbar_init(bar_s_full, 1);
     mbar_init(bar_p_full, 32 * kComputeWarps);
     mbar_init(bar_dp_full, 1);
@@ -190,31 +198,35 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       OtherBlock qb;
       while (cur.next(&qb)) {
         const int st = it & 1;
+        const uint32_t phase = (it >> 1) & 1;
         const int64_t row0 = stat_base + qb.row;
-        if (!mbar_wait(bar_q_empty, (it & 1) ^ 1, wctx, kWaitBwdLoad)) { ok = false; break; }
+        // The second stage holds V until the compute warps have moved it to TMEM.
+        if (it == 1 && !mbar_wait(bar_v_ready, 0, wctx, kWaitBwdLoad)) { ok = false; break; }
+        if (!mbar_wait(bar_q_empty + 8 * st, phase ^ 1, wctx, kWaitBwdLoad)) { ok = false; break; }
         if (lane == 0) {
-          mbar_expect_tx(bar_q_full, kQBytes);
+          mbar_expect_tx(bar_q_full + 8 * st, kQBytes);
 #pragma unroll
-          for (int h = 0; h < 4; ++h) tma_load_4d(smem_q + h * kQPanel, &map_q, bar_q_full, h * 64, head, qb.row, s.batch_coord);
+          for (int h = 0; h < 4; ++h)
+            tma_load_4d(smem_q + st * kStageStride + h * kQPanel, &map_q, bar_q_full + 8 * st, h * 64, head, qb.row, s.batch_coord);
         }
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
           const int r = lane + 32 * k;
-          if (row0 + r < p.rows) cp_async_4(smem_lse + st * 256 + r * 4, lse_head + row0 + r);
+          if (row0 + r < p.rows) {
+            // Both row statistics travel with the Q tile: its stage is released by the dK MMA, which comes after the
+            // dS phase has read them (the dO stage is released earlier, by the dV MMA).
+            cp_async_4(smem_lse + st * 256 + r * 4, lse_head + row0 + r);
+            cp_async_4(smem_dpsum + st * 256 + r * 4, dpsum_head + row0 + r);
+          }
         }
-        cp_async_arrive_noinc(bar_q_full);
-        if (!mbar_wait(bar_do_empty, (it & 1) ^ 1, wctx, kWaitBwdLoad)) { ok = false; break; }
+        cp_async_arrive_noinc(bar_q_full + 8 * st);
+        if (!mbar_wait(bar_do_empty + 8 * st, phase ^ 1, wctx, kWaitBwdLoad)) { ok = false; break; }
         if (lane == 0) {
-          mbar_expect_tx(bar_do_full, kQBytes);
+          mbar_expect_tx(bar_do_full + 8 * st, kQBytes);
 #pragma unroll
-          for (int h = 0; h < 4; ++h) tma_load_4d(smem_do + h * kQPanel, &map_do, bar_do_full, h * 64, head, qb.row, s.batch_coord);
+          for (int h = 0; h < 4; ++h)
+            tma_load_4d(smem_do + st * kStageStride + h * kQPanel, &map_do, bar_do_full + 8 * st, h * 64, head, qb.row, s.batch_coord);
         }
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          const int r = lane + 32 * k;
-          if (row0 + r < p.rows) cp_async_4(smem_dpsum + st * 256 + r * 4, dpsum_head + row0 + r);
-        }
-        cp_async_arrive_noinc(bar_do_full);
         ++it;
       }
     }
@@ -227,52 +239,79 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       constexpr uint32_t idesc_dq = umma_idesc_bf16(128, kSubM, 1, 1);  // dQ^T: A and B MN-major
       const uint32_t t_s = tmem_base + kTmemS, t_dp = tmem_base + kTmemDp;
       const uint32_t t_dv = tmem_base + kTmemDv, t_dk = tmem_base + kTmemDk;
-      const uint32_t q_half = smem_q + 2 * dh * kQPanel, do_half = smem_do + 2 * dh * kQPanel;
+      const uint32_t t_v = tmem_base + kTmemV;  // V of the key block as BF16, the A operand of dP^T
       const uint32_t k_half = smem_k + 2 * dh * kKvPanel;
-      auto mma_scores = [&](uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem) {  // D = A B^T over all 256 columns
+      // S^T = K Q^T over all 256 columns (both operands in shared memory)
+      auto issue_s = [&](uint32_t q_tile) {
 #pragma unroll
         for (int kk = 0; kk < 16; ++kk) {
           const uint32_t a_off = (kk >> 2) * kKvPanel + (kk & 3) * 32;
           const uint32_t b_off = (kk >> 2) * kQPanel + (kk & 3) * 32;
-          umma_ss(d_tmem, umma_smem_desc(a_smem + a_off, 16, 1024), umma_smem_desc(b_smem + b_off, 16, 1024), idesc_st, kk > 0);
+          umma_ss(t_s, umma_smem_desc(smem_k + a_off, 16, 1024), umma_smem_desc(q_tile + b_off, 16, 1024), idesc_st, kk > 0);
         }
-      };
-      bool ok = mbar_wait(bar_kv_full, 0, wctx, kWaitBwdMma);
-      for (int it = 0; ok && it < iterations; ++it) {
-        const uint32_t ph = it & 1;
-        // S^T
-        if (!mbar_wait(bar_q_full, ph, wctx, kWaitBwdMma)) { ok = false; break; }
-        tc_fence_after();
-        mma_scores(t_s, smem_k, smem_q);
         tc_commit(bar_s_full);
-        // dP^T (its TMEM columns hold dQ^T of the previous iteration until the drain warps have read it)
-        if (!mbar_wait(bar_do_full, ph, wctx, kWaitBwdMma)) { ok = false; break; }
-        if (it > 0 && !mbar_wait(bar_dq_empty, (it - 1) & 1, wctx, kWaitBwdMma)) { ok = false; break; }
-        tc_fence_after();
-        mma_scores(t_dp, smem_v, smem_do);
+      };
+      // dP^T = V dO^T with V read from TMEM: only dO comes from shared memory (2 KB per 32 tensor cycles)
+      auto issue_dp = [&](uint32_t do_tile) {
+#pragma unroll
+        for (int kk = 0; kk < 16; ++kk) {
+          const uint32_t b_off = (kk >> 2) * kQPanel + (kk & 3) * 32;
+          umma_ts(t_dp, t_v + kk * 8, umma_smem_desc(do_tile + b_off, 16, 1024), idesc_st, kk > 0);
+        }
         tc_commit(bar_dp_full);
+      };
+      bool ok = mbar_wait(bar_kv_full, 0, wctx, kWaitBwdMma) && mbar_wait(bar_q_full, 0, wctx, kWaitBwdMma);
+      if (ok) {
+        tc_fence_after();
+        issue_s(smem_q);
+        ok = mbar_wait(bar_do_full, 0, wctx, kWaitBwdMma) && mbar_wait(bar_v_ready, 0, wctx, kWaitBwdMma);
+      }
+      if (ok) {
+        tc_fence_after();
+        issue_dp(smem_do);
+      }
+      for (int it = 0; ok && it < iterations; ++it) {
+        const int st = it & 1;
+        const uint32_t phase = (it >> 1) & 1;
+        const uint32_t q_tile = smem_q + st * kStageStride, do_tile = smem_do + st * kStageStride;
+        const uint32_t q_half = q_tile + 2 * dh * kQPanel, do_half = do_tile + 2 * dh * kQPanel;
+        const bool more = it + 1 < iterations;
         // dV_h += P^T dO_h
-        if (!mbar_wait(bar_p_full, ph, wctx, kWaitBwdMma)) { ok = false; break; }
+        if (!mbar_wait(bar_p_full, it & 1, wctx, kWaitBwdMma)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           umma_ts(t_dv, t_s + kk * kCols, umma_smem_desc(do_half + kk * 2048, kQPanel, 1024), idesc_dv,
                   it > 0 || kk > 0);
-        tc_commit(bar_do_empty);
-        // dK_h += dS^T Q_h ; dQ_h^T = K_h^T dS^T
-        if (!mbar_wait(bar_ds_full, ph, wctx, kWaitBwdMma)) { ok = false; break; }
+        tc_commit(bar_do_empty + 8 * st);
+        // S^T of the next iteration (P^T of this one has been consumed by the MMAs above, which run first)
+        if (more) {
+          if (!mbar_wait(bar_q_full + 8 * (st ^ 1), ((it + 1) >> 1) & 1, wctx, kWaitBwdMma)) { ok = false; break; }
+          tc_fence_after();
+          issue_s(smem_q + (st ^ 1) * kStageStride);
+        }
+        // dQ_h^T = K_h^T dS^T first (its drain gates the next dP^T), then dK_h += dS^T Q_h
+        if (!mbar_wait(bar_ds_full, it & 1, wctx, kWaitBwdMma)) { ok = false; break; }
         tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_ss(t_dk, umma_smem_desc(smem_ds + kk * 32, 16, 1024), umma_smem_desc(q_half + kk * 2048, kQPanel, 1024), idesc_dk,
-                  it > 0 || kk > 0);
-        tc_commit(bar_q_empty);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           umma_ss(t_dp, umma_smem_desc(k_half + kk * 2048, kKvPanel, 1024), umma_smem_desc(smem_ds + kk * 2048, kDsBytes, 1024),
                   idesc_dq, kk > 0);
         tc_commit(bar_dq_full);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ss(t_dk, umma_smem_desc(smem_ds + kk * 32, 16, 1024), umma_smem_desc(q_half + kk * 2048, kQPanel, 1024), idesc_dk,
+                  it > 0 || kk > 0);
+        tc_commit(bar_q_empty + 8 * st);
         tc_commit(bar_ds_empty);
+        (void)phase;
+        // dP^T of the next iteration (its TMEM columns hold dQ^T until the drain warps have read it)
+        if (more) {
+          if (!mbar_wait(bar_do_full + 8 * (st ^ 1), ((it + 1) >> 1) & 1, wctx, kWaitBwdMma) ||
+              !mbar_wait(bar_dq_empty, it & 1, wctx, kWaitBwdMma)) { ok = false; break; }
+          tc_fence_after();
+          issue_dp(smem_do + (st ^ 1) * kStageStride);
+        }
       }
       if (ok) tc_commit(bar_final);
     }
@@ -293,6 +332,27 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const uint32_t ds_row = smem_ds + r * 128;
     int it = 0;
     bool ok = true;
+    if (iterations > 0) {
+      // V of the key block moves from its landing place in shared memory to TMEM (BF16 pairs, key row on the lane), where
+      // it is the A operand of every dP^T MMA; the shared memory becomes the second Q / dO stage. Group wg copies the
+      // 64 columns of panel wg: eight 16-byte chunks per row, stored with the 128-byte swizzle of the TMA box.
+      ok = mbar_wait_warp(bar_kv_full, 0, wctx, kWaitBwdCompute);
+      if (ok) {
+        uint32_t words[32];
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          const float4 chunk = ld_shared_f4(smem_v + wg * kKvPanel + r * 128 + ((ch ^ (r & 7)) << 4));
+          words[4 * ch + 0] = __float_as_uint(chunk.x);
+          words[4 * ch + 1] = __float_as_uint(chunk.y);
+          words[4 * ch + 2] = __float_as_uint(chunk.z);
+          words[4 * ch + 3] = __float_as_uint(chunk.w);
+        }
+        tmem_st32(tmem_base + lane_addr + kTmemV + 32 * wg, words);
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_v_ready);
+      }
+    }
     for (int g = 0; ok && g < group; ++g) {
       HalfBlockCursor cur;
       cur.init(&pr, seq, s, n0, c1);
