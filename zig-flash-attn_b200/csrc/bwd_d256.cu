@@ -21,8 +21,8 @@
 // and its S^T MMA overlap the current one.
 // Shared memory: K of the block (64 KB), two stages of a Q and a dO tile (32 KB each), the dS tile, two 8 KB staging
 // buffers.
-// Warps 0-15 compute P and dS (four groups, 16 query columns each), warps 16-19 drain dQ, warp 20 issues MMAs, warp 21
-// issues the loads.
+// Warps 0-15 compute P and dS (four groups, 16 query columns each), warps 16-23 drain dQ (two groups, 32 query rows
+// each), warp 24 issues MMAs, warp 25 issues the loads.
 #include "bwd_common.cuh"
 
 namespace b200fa {
@@ -32,10 +32,13 @@ constexpr int kSubM = 64;                   // query rows per iteration
 constexpr int kGroups = 4;                   // compute warpgroups: a thread handles one key row and 64 / kGroups query columns
 constexpr int kCols = kSubM / kGroups;
 constexpr int kComputeWarps = 4 * kGroups;
-constexpr int kMmaWarp = kComputeWarps + 4, kLoadWarp = kComputeWarps + 5;
-constexpr int kThreads = 32 * (kComputeWarps + 8);
-// registers per thread of the compute, drain and MMA/load warpgroups: 4 x 128 x 88 + 128 x 72 + 128 x 56 = 768 x 80
-constexpr int kRegsCompute = 88, kRegsDrain = 72, kRegsMisc = 56;
+constexpr int kDrains = 2;                   // dQ drain warpgroups: each takes half of the 64 query rows of an iteration
+constexpr int kMmaWarp = kComputeWarps + 4 * kDrains, kLoadWarp = kMmaWarp + 1;
+constexpr int kThreads = 32 * (kMmaWarp + 4);
+// registers per thread of the compute, drain and MMA/load warpgroups: 4 x 128 x 88 + 2 x 128 x 56 + 128 x 40 = 896 x 72
+constexpr int kRegsCompute = 88, kRegsDrain = 56, kRegsMisc = 40;
+static_assert(kComputeWarps * 32 * kRegsCompute + kDrains * 128 * kRegsDrain + 128 * kRegsMisc == kThreads * 72,
+              "the per-role register budgets must add up to the launch allocation");
 constexpr int kKvPanel = 128 * 128;         // 128 key rows x 64 columns BF16
 constexpr int kKvBytes = 4 * kKvPanel;      // 64 KB
 constexpr int kQPanel = kSubM * 128;        // 64 query rows x 64 columns BF16
@@ -147,7 +150,7 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     mbar_init(bar_ds_full, 32 * kComputeWarps);
     mbar_init(bar_ds_empty, 1);
     mbar_init(bar_dq_full, 1);
-    mbar_init(bar_dq_empty, 128);
+    mbar_init(bar_dq_empty, 128 * kDrains);
     mbar_init(bar_final, 1);
     fence_barrier_init();
   }
@@ -482,13 +485,17 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
   } else {
     setmaxnreg_dec<kRegsDrain>();
-    // ------------------------------------------------------------------ dQ drain (one warpgroup, thread = head-dim column)
+    // ------------------------------------------------------------------ dQ drain (two warpgroups, thread = head-dim column)
+    // Drain group dg takes query rows [32 dg, 32 dg + 32) of every iteration in two chunks of 16 through its own
+    // staging buffer.
+    const int dg = (warp - kComputeWarps) >> 2;
     const int d = (warp & 3) * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t t_dq = tmem_base + lane_addr + kTmemDp;
-    const bool leader = threadIdx.x == kComputeWarps * 32;
+    const uint32_t t_dq = tmem_base + lane_addr + kTmemDp + 2 * kStageRows * dg;
+    const uint32_t stage = smem_stage + dg * kStageBytes;
+    const bool leader = (warp & 3) == 0 && lane == 0;
+    constexpr int kChunks = kSubM / kStageRows / kDrains;
     int it = 0;
-    uint32_t chunks = 0;
     bool ok = true;
     for (int g = 0; ok && g < group; ++g) {
       const int head = kv_head * group + g;
@@ -496,31 +503,30 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       cur.init(&pr, seq, s, n0, c1);
       OtherBlock qb;
       while (cur.next(&qb)) {
-        const int row0 = (int)(stat_base + qb.row);
+        const int row0 = (int)(stat_base + qb.row) + 2 * kStageRows * dg;
         if (!mbar_wait(bar_dq_full, it & 1, wctx, kWaitBwdReduce)) { ok = false; break; }
         tc_fence_after();
+        // All 32 query columns of this group leave TMEM at once, so the next dP^T MMA can start while they are staged.
+        uint32_t acc[kChunks * kStageRows];
+        static_assert(kChunks * kStageRows == 32, "the drain reads its TMEM columns with one 32-column load");
+        tmem_ld32(t_dq, acc);
+        tc_wait_ld();
+        tc_fence_before();
+        mbar_arrive(bar_dq_empty);
 #pragma unroll
-        for (int ch = 0; ch < kSubM / kStageRows; ++ch) {
-          uint32_t acc[16];
-          tmem_ld16(t_dq + kStageRows * ch, acc);
-          tc_wait_ld();
-          if (ch == kSubM / kStageRows - 1) {
-            tc_fence_before();
-            mbar_arrive(bar_dq_empty);
-          }
-          const uint32_t stage = smem_stage + (chunks & 1) * kStageBytes;
-          if (leader) bulk_wait_group_read<1>();  // the copy that read this buffer two chunks ago is done with it
-          named_barrier_sync(1, 128);
+        for (int ch = 0; ch < kChunks; ++ch) {
+          if (leader) bulk_wait_group_read<0>();  // the copy that read the staging buffer last is done with it
+          named_barrier_sync(1 + dg, 128);
           // Transpose: this thread holds column d of 16 query rows; the staging buffer is (query row, column) row-major.
 #pragma unroll
-          for (int i = 0; i < kStageRows; ++i) st_shared_f32(stage + i * 512 + d * 4, __uint_as_float(acc[i]));
+          for (int i = 0; i < kStageRows; ++i)
+            st_shared_f32(stage + i * 512 + d * 4, __uint_as_float(acc[kStageRows * ch + i]));
           fence_proxy_async_smem();
-          named_barrier_sync(1, 128);
+          named_barrier_sync(1 + dg, 128);
           if (leader) {
             tma_reduce_add_4d(&map_dq, stage, dh * 128, head, row0 + kStageRows * ch, 0);
             bulk_commit_group();
           }
-          ++chunks;
         }
         ++it;
       }
