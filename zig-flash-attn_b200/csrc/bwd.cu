@@ -263,6 +263,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         // dV += P^T dO
         if (!mbar_wait_traced(bar_p_full, it & 1, wctx, kWaitBwdMma, 2, false)) { ok = false; break; }
         tc_fence_after();
+        trace_event(wctx, traced_cta && it < 10, 0, trace_n, 50 + it);  // P(it) complete
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           umma_ts(t_dv, t_s + (Cfg::kGroups == 2 ? (kk >> 2) * 64 + (kk & 3) * 8 : (kk >> 1) * 32 + (kk & 1) * 8),
@@ -279,6 +280,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         }
         // dK += dS^T Q ; dQ = dS K
         if (!mbar_wait_traced(bar_ds_full, it & 1, wctx, kWaitBwdMma, 4, false)) { ok = false; break; }
+        trace_event(wctx, traced_cta && it < 10, 0, trace_n, 250 + it);  // dS(it) complete
         const int dq_buf = Cfg::kDqBuffers == 2 ? (it & 1) : 0;
         if (Cfg::kDqBuffers == 2 && it >= 2 &&
             !mbar_wait(bar_dq_empty + dq_buf * kDqBarStep, ((it >> 1) - 1) & 1, wctx, kWaitBwdMma)) { ok = false; break; }
@@ -353,7 +355,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         if (!mbar_wait_traced(bar_s_full, it & 1, wctx, kWaitBwdCompute, 7, true)) { ok = false; break; }
         tc_fence_after();
         const long long t_p = trace_clock(wctx);
-        trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 500 + it);  // S ready
+        trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 500 + it);
+        trace_event(wctx, traced_cta && threadIdx.x == 32 * Cfg::kComputeWarps - 32 && it < 10, 4, trace_n, 1500 + it);  // S ready
         float pf[C];
         tmem_ld32(t_s + cb, reinterpret_cast<uint32_t*>(pf));
         if constexpr (C == 64) tmem_ld32(t_s + cb + 32, reinterpret_cast<uint32_t*>(pf) + 32);
@@ -389,14 +392,16 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         tc_fence_before();
         mbar_arrive(bar_p_full);
         trace_add(wctx, 13, trace_clock(wctx) - t_p);
-        trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 600 + it);  // P stored
+        trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 600 + it);
+        trace_event(wctx, traced_cta && threadIdx.x == 32 * Cfg::kComputeWarps - 32 && it < 10, 4, trace_n, 1600 + it);  // P stored
         // ---- dS^T = P^T o (dP^T - D), written to shared memory as BF16
         if (!mbar_wait_traced(bar_dp_full, it & 1, wctx, kWaitBwdCompute, 8, true)) { ok = false; break; }
         // The dS tile of the previous iteration must have been consumed by its dK and dQ MMAs.
         if (it > 0 && !mbar_wait_traced(bar_ds_empty, (it - 1) & 1, wctx, kWaitBwdCompute, 9, true)) { ok = false; break; }
         tc_fence_after();
         const long long t_ds = trace_clock(wctx);
-        trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 700 + it);  // dP ready
+        trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 700 + it);
+        trace_event(wctx, traced_cta && threadIdx.x == 32 * Cfg::kComputeWarps - 32 && it < 10, 4, trace_n, 1700 + it);  // dP ready
 #pragma unroll
         for (int h = 0; h < C / 32; ++h) {
           float dp[32];
@@ -431,7 +436,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         fence_proxy_async_smem();
         mbar_arrive(bar_ds_full);
         trace_add(wctx, 14, trace_clock(wctx) - t_ds);
-        trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 800 + it);  // dS stored
+        trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 800 + it);
+        trace_event(wctx, traced_cta && threadIdx.x == 32 * Cfg::kComputeWarps - 32 && it < 10, 4, trace_n, 1800 + it);  // dS stored
         ++it;
       }
     }
@@ -503,6 +509,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         const uint32_t dq_phase = Cfg::kDqBuffers == 2 ? (it >> 1) & 1 : it & 1;
         if (!mbar_wait_traced(bar_dq_full + dq_buf * kDqBarStep, dq_phase, wctx, kWaitBwdReduce, 10, true)) { ok = false; break; }
         tc_fence_after();
+        trace_event(wctx, traced_cta && leader && dg == 0 && it < 10, 2, trace_n, 9100 + it);  // dQ ready
         const uint32_t t_dq = t_dq0 + dq_buf * D;
 #pragma unroll
         for (int c0 = 0; c0 < kChunks; ++c0) {
@@ -510,6 +517,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           uint32_t acc[32];
           tmem_ld32(t_dq + 32 * ch, acc);
           tc_wait_ld();
+          trace_event(wctx, traced_cta && leader && dg == 0 && it < 10 && c0 == 0, 2, trace_n, 9200 + it);  // first chunk in registers
           if (c0 == kChunks - 1) {
             tc_fence_before();
             mbar_arrive(bar_dq_empty + dq_buf * kDqBarStep);
@@ -529,6 +537,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           if (leader) {
             tma_reduce_add_4d(&map_dq, stage, 32 * ch, head, row0, 0);
             bulk_commit_group();
+            trace_event(wctx, traced_cta && dg == 0 && it < 10 && c0 == 0, 2, trace_n, 9300 + it);  // first chunk staged
           }
           ++chunks;
         }

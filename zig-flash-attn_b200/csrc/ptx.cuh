@@ -107,9 +107,15 @@ constexpr bool kTraceBuild = true;
 #else
 constexpr bool kTraceBuild = false;
 #endif
+// -DB200FA_TRACE_SUMS=0 leaves the per-wait sums out of a tuning build: their atomics (every warp of every CTA on a few
+// addresses) stretch the iterations, which a per-role timeline (trace_event) must not see.
+#ifndef B200FA_TRACE_SUMS
+#define B200FA_TRACE_SUMS 1
+#endif
+constexpr bool kTraceSums = B200FA_TRACE_SUMS != 0;
 __device__ __forceinline__ bool mbar_wait_traced(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int code, int slot,
                                                  bool warp_uniform) {
-  if (!kTraceBuild || ctx.trace == nullptr) {
+  if (!kTraceBuild || !kTraceSums || ctx.trace == nullptr) {
     const bool done = mbar_wait(bar, parity, ctx, code);
     return warp_uniform ? __all_sync(0xffffffffu, done) : done;
   }
@@ -132,7 +138,7 @@ __device__ __forceinline__ void trace_event(const WaitCtx& ctx, bool selected, i
   }
 }
 __device__ __forceinline__ void trace_add(const WaitCtx& ctx, int slot, long long cycles) {
-  if (kTraceBuild && ctx.trace != nullptr && (threadIdx.x & 31) == 0)
+  if (kTraceBuild && kTraceSums && ctx.trace != nullptr && (threadIdx.x & 31) == 0)
     atomicAdd(reinterpret_cast<unsigned long long*>(ctx.trace + slot), static_cast<unsigned long long>(cycles));
 }
 // Same, with a warp-uniform result (for code that goes on to execute .sync.aligned instructions).

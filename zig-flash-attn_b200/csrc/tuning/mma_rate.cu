@@ -1,0 +1,88 @@
+// Tuning microbenchmark (not part of the library): cycles per tcgen05.mma (kind::f16, BF16 -> FP32, cta_group::1,
+// M = 128, K = 16) for several N, operand sources, operand majorness and accumulator patterns. One CTA on each of
+// `ctas` SMs; thread 0 issues `count` MMAs back to back on zeroed operands, commits, and waits (bounded) for the commit.
+//   nvcc -gencode arch=compute_100a,code=sm_100a -O3 -std=c++17 -o mma_rate zig-flash-attn_b200/csrc/tuning/mma_rate.cu
+//   ./mma_rate
+#include <cstdio>
+#include <cuda_runtime.h>
+#include "../ptx.cuh"
+using namespace b200fa;
+
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity) {
+  for (int i = 0; i < 4000000; ++i) if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+
+template <int N, int MODE>  // MODE 0: SS, both operands K-major, one accumulator; 1: the same with two accumulators in turn; 2: TS (A in TMEM);
+                             // 3: SS with B MN-major; 4: SS with A and B MN-major
+__global__ void __launch_bounds__(128, 1) rate_kernel(long long* out, int count) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t base = smem_u32(smem);
+  const uint32_t bar = base + 200 * 1024, slot = bar + 16;
+  for (int i = threadIdx.x; i < 200 * 1024 / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(smem)[i] = 0;
+  if (threadIdx.x == 0) { mbar_init(bar, 1); fence_barrier_init(); }
+  if (threadIdx.x < 32) { tmem_alloc(slot, 512); tmem_relinquish(); }
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(smem + 200 * 1024 + 16);
+  if (threadIdx.x == 0) {
+    constexpr uint32_t idesc = umma_idesc_bf16(128, N, MODE == 4 ? 1 : 0, MODE >= 3 ? 1 : 0);
+    const uint32_t a = base, b = base + 64 * 1024;
+    for (int rep = 0; rep < 3; ++rep) {
+      const long long t0 = clock64();
+      for (int i = 0; i < count; ++i) {
+        const uint32_t off = (i & 3) * 32 + ((i >> 2) & 1) * 16384;
+        const uint32_t d = tmem + ((MODE == 1 && (i & 1)) ? 256 : 0);
+        if (MODE == 2) umma_ts(d, tmem + 256 + (i & 7) * 8, umma_smem_desc(b + off, 16, 1024), idesc, i > 1);
+        else if (MODE == 4) umma_ss(d, umma_smem_desc(a + (i & 7) * 2048, 16384, 1024), umma_smem_desc(b + (i & 7) * 2048, 16384, 1024), idesc, i > 1);
+        else if (MODE == 3) umma_ss(d, umma_smem_desc(a + off, 16, 1024), umma_smem_desc(b + (i & 7) * 2048, 16384, 1024), idesc, i > 1);
+        else umma_ss(d, umma_smem_desc(a + off, 16, 1024), umma_smem_desc(b + off, 16, 1024), idesc, i > 1);
+      }
+      const long long t1 = clock64();
+      tc_commit(bar);
+      const bool ok = wait_bar(bar, rep & 1);
+      const long long t2 = clock64();
+      if (blockIdx.x == 0) { out[3 * rep] = t1 - t0; out[3 * rep + 1] = t2 - t0; out[3 * rep + 2] = ok; }
+      if (!ok) break;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (threadIdx.x < 32) tmem_dealloc(tmem, 512);
+}
+
+template <int N, int MODE>
+void run(const char* name, int ctas, int count) {
+  long long* out; cudaMalloc(&out, 128); cudaMemset(out, 0, 128);
+  const int smem = 200 * 1024 + 64;
+  cudaFuncSetAttribute(rate_kernel<N, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  rate_kernel<N, MODE><<<ctas, 128, smem>>>(out, count);
+  cudaError_t e = cudaDeviceSynchronize();
+  long long h[9]; cudaMemcpy(h, out, sizeof(h), cudaMemcpyDeviceToHost);
+  printf("%-34s ctas %3d: issue %6.1f  total %6.1f cycles per MMA (ok %lld) %s\n", name, ctas, double(h[6]) / count, double(h[7]) / count,
+         h[8], e == cudaSuccess ? "" : cudaGetErrorString(e));
+  cudaFree(out);
+}
+
+int main() {
+  const int count = 512;
+  for (int ctas : {1, 148}) {
+    run<64, 0>("SS N=64 one accumulator", ctas, count);
+    run<128, 0>("SS N=128 one accumulator", ctas, count);
+    run<256, 0>("SS N=256 one accumulator", ctas, count);
+    run<128, 1>("SS N=128 two accumulators", ctas, count);
+    run<64, 1>("SS N=64 two accumulators", ctas, count);
+    run<64, 2>("TS N=64", ctas, count);
+    run<128, 2>("TS N=128", ctas, count);
+    run<256, 2>("TS N=256 (acc over A: timing only)", ctas, count);
+    run<64, 3>("SS N=64 B MN-major", ctas, count);
+    run<128, 3>("SS N=128 B MN-major", ctas, count);
+    run<256, 3>("SS N=256 B MN-major", ctas, count);
+    run<64, 4>("SS N=64 A and B MN-major", ctas, count);
+    run<128, 4>("SS N=128 A and B MN-major", ctas, count);
+  }
+  return 0;
+}
