@@ -45,7 +45,7 @@ struct BwdConfig {
   static constexpr int kOffStage = kOffDs + kDsBytes;    // two staging buffers
   static constexpr int kOffStats = kOffStage + 2 * kStageBytes;  // lse[2][128], dpsum[2][128] floats
   static constexpr int kOffBars = kOffStats + 4 * 512;
-  static constexpr int kSmemBytes = kOffBars + 160;
+  static constexpr int kSmemBytes = kOffBars + 128;
   // Compute warpgroups (P, dS): each thread handles one key row and 128 / kGroups query columns.
   // Four groups of 32 columns instead of two of 64 halve the latency of the P and dS phases, which sit on the serial
   // chain of an iteration (989 against 880 TF/s on batch 4, seqlen 8192, heads 32/8, causal).
@@ -66,11 +66,6 @@ struct BwdConfig {
   static_assert(kGroups == 2 || kGroups == 4, "two or four compute warpgroups");
   static constexpr int kThreads = 32 * (kComputeWarps + 4 * kDrains + 4);  // + 1 dQ-drain warpgroup, 1 warpgroup with the MMA and load warps
   static constexpr int kTmemS = 0, kTmemDp = 128, kTmemDv = 256, kTmemDk = 256 + D;
-  // dQ accumulator: at head_dim 128 the 512 TMEM columns are full and dQ lies over dP^T, so the next dP^T MMA waits for
-  // the drain; at head_dim 64 the columns [384, 512) are free and hold two dQ accumulators used in turn, which takes
-  // the drain off the serial chain of an iteration.
-  static constexpr int kDqBuffers = D == 64 ? 2 : 1;
-  static constexpr int kTmemDq = D == 64 ? 384 : kTmemDp;
 };
 
 template <int D>
@@ -115,7 +110,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   const uint32_t bar_do_full = bars + 40, bar_do_empty = bars + 48, bar_s_full = bars + 56, bar_p_full = bars + 64;
   const uint32_t bar_dp_full = bars + 72, bar_ds_full = bars + 80, bar_dq_full = bars + 88, bar_dq_empty = bars + 96;
   const uint32_t bar_final = bars + 104, bar_ds_empty = bars + 120;
-  constexpr uint32_t kDqBarStep = 40;  // the barriers of the second dQ accumulator: bars + 128 (full), bars + 136 (empty)
   const uint32_t tmem_slot = bars + 112, abort_slot = bars + 116;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + (abort_slot - smem_u32(smem_raw)));
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
@@ -141,8 +135,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     mbar_init(bar_ds_full, 32 * Cfg::kComputeWarps);
     mbar_init(bar_dq_full, 1);
     mbar_init(bar_dq_empty, 128 * Cfg::kDrains);
-    mbar_init(bar_dq_full + kDqBarStep, 1);
-    mbar_init(bar_dq_empty + kDqBarStep, 128 * Cfg::kDrains);
     mbar_init(bar_final, 1);
     mbar_init(bar_ds_empty, 1);
     fence_barrier_init();
@@ -280,17 +272,14 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         }
         // dK += dS^T Q ; dQ = dS K
         if (!mbar_wait_traced(bar_ds_full, it & 1, wctx, kWaitBwdMma, 4, false)) { ok = false; break; }
-        trace_event(wctx, traced_cta && it < 10, 0, trace_n, 250 + it);  // dS(it) complete
-        const int dq_buf = Cfg::kDqBuffers == 2 ? (it & 1) : 0;
-        if (Cfg::kDqBuffers == 2 && it >= 2 &&
-            !mbar_wait(bar_dq_empty + dq_buf * kDqBarStep, ((it >> 1) - 1) & 1, wctx, kWaitBwdMma)) { ok = false; break; }
         tc_fence_after();
+        trace_event(wctx, traced_cta && it < 10, 0, trace_n, 250 + it);  // dS(it) complete
         auto issue_dq = [&]() {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            umma_ss(tmem_base + Cfg::kTmemDq + dq_buf * D, umma_smem_desc(smem_ds + kk * 2048, Cfg::kPanelBytes, 1024),
+            umma_ss(t_dp, umma_smem_desc(smem_ds + kk * 2048, Cfg::kPanelBytes, 1024),
                     umma_smem_desc(smem_k + kk * 2048, Cfg::kPanelBytes, 1024), idesc_dq, kk > 0);
-          tc_commit(bar_dq_full + dq_buf * kDqBarStep);
+          tc_commit(bar_dq_full);
         };
         auto issue_dk = [&]() {
 #pragma unroll
@@ -309,7 +298,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         // dP^T of the next iteration (its TMEM columns hold dQ until the reduce warps have drained it)
         if (more) {
           if (!mbar_wait_traced(bar_do_full, (it + 1) & 1, wctx, kWaitBwdMma, 5, false) ||
-              (Cfg::kDqBuffers == 1 && !mbar_wait_traced(bar_dq_empty, it & 1, wctx, kWaitBwdMma, 6, false))) { ok = false; break; }
+              !mbar_wait_traced(bar_dq_empty, it & 1, wctx, kWaitBwdMma, 6, false)) { ok = false; break; }
           tc_fence_after();
           trace_event(wctx, traced_cta && it < 10, 0, trace_n, 350 + it);  // dO(it+1) and dQ drain ready
           mma_kmajor(t_dp, smem_v, smem_do);
@@ -355,8 +344,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         if (!mbar_wait_traced(bar_s_full, it & 1, wctx, kWaitBwdCompute, 7, true)) { ok = false; break; }
         tc_fence_after();
         const long long t_p = trace_clock(wctx);
-        trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 500 + it);
-        trace_event(wctx, traced_cta && threadIdx.x == 32 * Cfg::kComputeWarps - 32 && it < 10, 4, trace_n, 1500 + it);  // S ready
+        trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 500 + it);  // S ready
+        trace_event(wctx, traced_cta && threadIdx.x == 32 * Cfg::kComputeWarps - 32 && it < 10, 4, trace_n, 1500 + it);  // the same from the last compute warp
         float pf[C];
         tmem_ld32(t_s + cb, reinterpret_cast<uint32_t*>(pf));
         if constexpr (C == 64) tmem_ld32(t_s + cb + 32, reinterpret_cast<uint32_t*>(pf) + 32);
@@ -392,16 +381,16 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         tc_fence_before();
         mbar_arrive(bar_p_full);
         trace_add(wctx, 13, trace_clock(wctx) - t_p);
-        trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 600 + it);
-        trace_event(wctx, traced_cta && threadIdx.x == 32 * Cfg::kComputeWarps - 32 && it < 10, 4, trace_n, 1600 + it);  // P stored
+        trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 600 + it);  // P stored
+        trace_event(wctx, traced_cta && threadIdx.x == 32 * Cfg::kComputeWarps - 32 && it < 10, 4, trace_n, 1600 + it);  // the same from the last compute warp
         // ---- dS^T = P^T o (dP^T - D), written to shared memory as BF16
         if (!mbar_wait_traced(bar_dp_full, it & 1, wctx, kWaitBwdCompute, 8, true)) { ok = false; break; }
         // The dS tile of the previous iteration must have been consumed by its dK and dQ MMAs.
         if (it > 0 && !mbar_wait_traced(bar_ds_empty, (it - 1) & 1, wctx, kWaitBwdCompute, 9, true)) { ok = false; break; }
         tc_fence_after();
         const long long t_ds = trace_clock(wctx);
-        trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 700 + it);
-        trace_event(wctx, traced_cta && threadIdx.x == 32 * Cfg::kComputeWarps - 32 && it < 10, 4, trace_n, 1700 + it);  // dP ready
+        trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 700 + it);  // dP ready
+        trace_event(wctx, traced_cta && threadIdx.x == 32 * Cfg::kComputeWarps - 32 && it < 10, 4, trace_n, 1700 + it);  // the same from the last compute warp
 #pragma unroll
         for (int h = 0; h < C / 32; ++h) {
           float dp[32];
@@ -436,8 +425,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         fence_proxy_async_smem();
         mbar_arrive(bar_ds_full);
         trace_add(wctx, 14, trace_clock(wctx) - t_ds);
-        trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 800 + it);
-        trace_event(wctx, traced_cta && threadIdx.x == 32 * Cfg::kComputeWarps - 32 && it < 10, 4, trace_n, 1800 + it);  // dS stored
+        trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 800 + it);  // dS stored
+        trace_event(wctx, traced_cta && threadIdx.x == 32 * Cfg::kComputeWarps - 32 && it < 10, 4, trace_n, 1800 + it);  // the same from the last compute warp
         ++it;
       }
     }
@@ -489,7 +478,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     // ------------------------------------------------------------------ dQ drain (one warpgroup, thread = query row)
     const int r = (warp & 3) * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t t_dq0 = tmem_base + lane_addr + Cfg::kTmemDq;
+    const uint32_t t_dq = tmem_base + lane_addr + Cfg::kTmemDp;
     // Drain warpgroup `dg` takes the columns [dg * D / kDrains, (dg + 1) * D / kDrains) of dQ; with two groups each has one
     // staging buffer of its own and the accumulator is released after one staging step instead of three.
     const int dg = (warp - Cfg::kComputeWarps) >> 2;
@@ -505,22 +494,18 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       OtherBlock qb;
       while (cur.next(&qb)) {
         const int row0 = (int)(stat_base + qb.row);
-        const int dq_buf = Cfg::kDqBuffers == 2 ? (it & 1) : 0;
-        const uint32_t dq_phase = Cfg::kDqBuffers == 2 ? (it >> 1) & 1 : it & 1;
-        if (!mbar_wait_traced(bar_dq_full + dq_buf * kDqBarStep, dq_phase, wctx, kWaitBwdReduce, 10, true)) { ok = false; break; }
+        if (!mbar_wait_traced(bar_dq_full, it & 1, wctx, kWaitBwdReduce, 10, true)) { ok = false; break; }
         tc_fence_after();
         trace_event(wctx, traced_cta && leader && dg == 0 && it < 10, 2, trace_n, 9100 + it);  // dQ ready
-        const uint32_t t_dq = t_dq0 + dq_buf * D;
 #pragma unroll
         for (int c0 = 0; c0 < kChunks; ++c0) {
           const int ch = dg * kChunks + c0;
           uint32_t acc[32];
           tmem_ld32(t_dq + 32 * ch, acc);
           tc_wait_ld();
-          trace_event(wctx, traced_cta && leader && dg == 0 && it < 10 && c0 == 0, 2, trace_n, 9200 + it);  // first chunk in registers
           if (c0 == kChunks - 1) {
             tc_fence_before();
-            mbar_arrive(bar_dq_empty + dq_buf * kDqBarStep);
+            mbar_arrive(bar_dq_empty);
             trace_event(wctx, traced_cta && leader && dg == 0 && it < 10, 2, trace_n, 900 + it);  // dQ drained
           }
           const uint32_t stage = smem_stage + (Cfg::kDrains == 2 ? dg : (chunks & 1)) * Cfg::kStageBytes;
@@ -528,16 +513,18 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             if (Cfg::kDrains == 2) bulk_wait_group_read<0>(); else bulk_wait_group_read<1>();
           }
           named_barrier_sync(1 + dg, 128);
+          trace_event(wctx, traced_cta && leader && dg == 0 && it < 10 && c0 == 0, 2, trace_n, 9400 + it);  // staging buffer free
           const uint32_t row_addr = stage + r * 128;
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             st_shared_v4(row_addr + ((j ^ (r & 7)) << 4), acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+          trace_event(wctx, traced_cta && leader && dg == 0 && it < 10 && c0 == 0, 2, trace_n, 9500 + it);  // stores issued
           fence_proxy_async_smem();
           named_barrier_sync(1 + dg, 128);
           if (leader) {
             tma_reduce_add_4d(&map_dq, stage, 32 * ch, head, row0, 0);
             bulk_commit_group();
-            trace_event(wctx, traced_cta && dg == 0 && it < 10 && c0 == 0, 2, trace_n, 9300 + it);  // first chunk staged
+            trace_event(wctx, traced_cta && dg == 0 && it < 10 && c0 == 0, 2, trace_n, 9300 + it);  // first chunk handed to the reduce-add
           }
           ++chunks;
         }
