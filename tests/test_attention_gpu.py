@@ -85,6 +85,23 @@ def test_narrow_windows(window):
         assert torch.equal(out, v)
 
 
+@pytest.mark.parametrize("head_dim", [64, 128, 256])
+@pytest.mark.parametrize("causal", [False, True])
+def test_reference_maximum_moves_in_later_key_blocks(head_dim, causal):
+    """Key norms grow ninefold along the sequence, so the row maximum keeps rising by far more than the lazy-rescale
+    threshold (8 in log2 units) in key blocks after the first: the running sum and the output accumulator are rescaled
+    in the middle of a row (reference zig/flash_fwd_sm100.zig:963-976 for the rescale rule)."""
+    torch.manual_seed(head_dim + causal)
+    seqlen_q, seqlen_k = 512, 1024
+    ramp = 1 + 8 * torch.arange(seqlen_k, device="cuda")[None, :, None, None] / seqlen_k
+    q = randn(2, seqlen_q, 4, head_dim, requires_grad=True)
+    k = (torch.randn(2, seqlen_k, 2, head_dim, device="cuda") * ramp).bfloat16().requires_grad_(True)
+    v = randn(2, seqlen_k, 2, head_dim, requires_grad=True)
+    dout = randn(2, seqlen_q, 4, head_dim)
+    results = run_fixed(q, k, v, dout, causal=causal)
+    parity.check_fixed(results, q.detach(), k.detach(), v.detach(), dout, causal, (-1, -1), notes=f"[growing keys d{head_dim}]")
+
+
 def test_rows_without_keys_are_zero():
     # causal with more queries than keys: the first seqlen_q - seqlen_k rows see nothing
     q, k, v = randn(2, 300, 4, 128, requires_grad=True), randn(2, 40, 2, 128, requires_grad=True), randn(2, 40, 2, 128, requires_grad=True)
