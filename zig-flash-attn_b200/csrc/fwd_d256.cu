@@ -54,7 +54,8 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   tiles.place(bars + 256);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + (abort_slot - smem_u32(smem_raw)));
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
-  const WaitCtx wctx{abort_flag, p.status, nullptr};
+  const WaitCtx wctx{abort_flag, p.status, p.trace};
+  int trace_n = 0;  // timeline of the first work item of CTA 0 (tuning builds)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -107,6 +108,7 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         mbar_expect_tx(bar_k_full, kKBytes);
 #pragma unroll
         for (int h = 0; h < 4; ++h) tma_load_4d(smem_k + h * kKPanel, &map_k, bar_k_full, h * 64, head, row, batch_coord);
+        trace_event(wctx, blockIdx.x == 0 && q_count == 1, 3, trace_n, 1000 + (k_count % 100));  // K load issued
         ++k_count;
         return true;
       };
@@ -117,6 +119,7 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         mbar_expect_tx(bar, kVBytes);
 #pragma unroll
         for (int h = 0; h < 4; ++h) tma_load_4d(smem_v + slot * kVBytes + h * kVPanel, &map_v, bar, h * 64, head, row, batch_coord);
+        trace_event(wctx, blockIdx.x == 0 && q_count == 1, 3, trace_n, 1100 + (v_count % 100));  // V half load issued
         ++v_count;
         return true;
       };
@@ -160,6 +163,7 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // S = Q K^T into score buffer `buffer`; the K slot is released when these MMAs have completed.
       auto issue_s = [&](int buffer) -> bool {
         if (!mbar_wait(bar_k_full, k_count & 1, wctx, kWaitKvFull)) return false;
+        trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 200 + (k_count % 100));  // K present
         ++k_count;
         tc_fence_after();
 #pragma unroll
@@ -169,6 +173,7 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         tc_commit(bar_k_empty);
         tc_commit(bar_s_full + 8 * buffer);
+        trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 100 + ((k_count - 1) % 100));  // S issued
         return true;
       };
       // O += P[:, 64 h .. 64 h + 64) V_half: the next V slot of the ring holds those 64 keys.
@@ -199,11 +204,15 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           const int buffer = n & 1;
           // keys [64,128) first: their probabilities are stored first
           if (!mbar_wait(bar_p_half + 8 * buffer, p_phase[buffer], wctx, kWaitPFull)) { ok = false; break; }
+          trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 300 + (n % 100));  // first half of P present
           if (!issue_pv_half(buffer, 1, n > 0)) { ok = false; break; }
+          trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 400 + (n % 100));  // PV of the first half issued
           if (!mbar_wait(bar_p_full + 8 * buffer, p_phase[buffer], wctx, kWaitPFull)) { ok = false; break; }
+          trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 500 + (n % 100));  // all of P present
           p_phase[buffer] ^= 1;
           if (!issue_pv_half(buffer, 0, true)) { ok = false; break; }
           tc_commit(bar_pv_done);
+          trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 600 + (n % 100));  // PV of the second half issued
           if (n + 2 < n_blocks) ok = issue_s(buffer);
         }
         if (ok) tc_commit(bar_q_empty);
@@ -235,6 +244,8 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (!mbar_wait_warp(bar_s_full + 8 * buffer, s_phase[buffer], wctx, kWaitSFull)) { ok = false; break; }
         s_phase[buffer] ^= 1;
         tc_fence_after();
+        const bool traced = blockIdx.x == 0 && threadIdx.x == 0 && popped == 1;
+        trace_event(wctx, traced, 1, trace_n, 2000 + (tile_blocks % 100));  // scores present
         int lo, hi;
         if (kb.banded) {
           lo = band_lo - kb.col0;
@@ -277,6 +288,7 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tc_wait_ld();
         if (masked) apply_mask(high, 64);
         const float m_new = fmaxf(m, fmaxf(max_low, max_of(high)));
+        trace_event(wctx, traced, 1, trace_n, 2100 + (tile_blocks % 100));  // row maximum known
         const bool grow = (m_new - m) * scale_log2 > 8.f;  // also true when m is -inf and m_new is finite
         if (__any_sync(0xffffffffu, grow)) {
           float alpha = 1.f;
@@ -327,10 +339,12 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar_p_half + 8 * buffer);  // keys [64,128): their half of the PV product may start
+        trace_event(wctx, traced, 1, trace_n, 2200 + (tile_blocks % 100));  // first half of P stored
         tc_wait_ld();
         if (masked) apply_mask(low, 0);
         exponentiate(low, 0);
         l += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
+        trace_event(wctx, traced, 1, trace_n, 2300 + (tile_blocks % 100));  // second half exponentiated
         // Observe the PV product of the previous block before releasing this one: the scores of block n only prove that
         // PV(n - 2) has completed, and a parity wait cannot tell a barrier that is two completions behind from one that
         // is done.
@@ -338,6 +352,7 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar_p_full + 8 * buffer);
+        trace_event(wctx, traced, 1, trace_n, 2400 + (tile_blocks % 100));  // all of P stored
         ++blocks;
         ++tile_blocks;
       }
