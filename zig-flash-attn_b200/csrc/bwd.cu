@@ -229,9 +229,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       constexpr uint32_t idesc_dq = umma_idesc_bf16(128, D, 1, 1);     // dQ: A MN-major, B MN-major
       const uint32_t t_s = tmem_base + Cfg::kTmemS, t_dp = tmem_base + Cfg::kTmemDp;
       const uint32_t t_dv = tmem_base + Cfg::kTmemDv, t_dk = tmem_base + Cfg::kTmemDk;
+      const int k_steps = (p.head_dim + 15) / 16;  // 16-column steps of the products over head_dim that hold data
       auto mma_kmajor = [&](uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem) {  // D = A B^T over head_dim
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
+          if (kk >= k_steps) break;  // head dims below the compiled width: the remaining columns are zero-filled
           const uint32_t off = (kk >> 2) * Cfg::kPanelBytes + (kk & 3) * 32;
           umma_ss(d_tmem, umma_smem_desc(a_smem + off, 16, 1024), umma_smem_desc(b_smem + off, 16, 1024), idesc_st, kk > 0);
         }

@@ -163,10 +163,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       constexpr uint32_t idesc_pv = umma_idesc_bf16(kBlockM, D, 0, 1);
       uint32_t ring = 0, q_count = 0, blocks = 0;
       bool ok = true;
+      const int k_steps = (p.head_dim + 15) / 16;  // 16-column steps of the score product that hold data
       auto issue_s = [&](int stage, uint32_t k_smem) {
         const uint32_t q_addr = smem_q + stage * Cfg::kTileBytes;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
+          if (kk >= k_steps) break;  // head dims below the compiled width: the remaining columns are zero-filled
           const uint32_t off = (kk >> 2) * Cfg::kPanelBytes + (kk & 3) * 32;
           umma_ss(tmem_base + Cfg::kTmemS + stage * 128, umma_smem_desc(q_addr + off, 16, 1024),
                   umma_smem_desc(k_smem + off, 16, 1024), idesc_s, kk > 0);
