@@ -368,3 +368,50 @@ def test_head_dim_512_varlen_forward_and_backward_refusal():
     out = zigfa.flash_attn_func(leaf, leaf.detach(), leaf.detach(), causal=True)
     with pytest.raises(ValueError, match="head_dim"):
         out.sum().backward()
+
+PAIR_SCRIPT = """
+import sys, torch
+sys.path.insert(0, sys.argv[1])
+import zigfa
+torch.manual_seed(5)
+results = {}
+for name, (batch, seqlen_q, seqlen_k, heads_q, heads_kv, options) in {
+    "dense": (2, 700, 1000, 4, 2, {}), "causal": (1, 2048, 2048, 4, 1, {"causal": True}), "window": (2, 1023, 1024, 2, 2, {"window_size": (300, 17)}),
+    "short": (3, 100, 3, 2, 1, {}),
+}.items():
+    q = torch.randn(batch, seqlen_q, heads_q, 256, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(batch, seqlen_k, heads_kv, 256, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(batch, seqlen_k, heads_kv, 256, device="cuda", dtype=torch.bfloat16)
+    out, lse = zigfa.flash_attn_func(q, k, v, return_attn_probs=True, **options)
+    results[name] = (out.cpu(), lse.cpu())
+lengths = torch.tensor([0, 300, 1, 513, 128], dtype=torch.int32)
+cu = torch.nn.functional.pad(lengths.cumsum(0), (1, 0)).int().cuda()
+total = int(lengths.sum())
+q = torch.randn(total, 4, 256, device="cuda", dtype=torch.bfloat16)
+k = torch.randn(total, 2, 256, device="cuda", dtype=torch.bfloat16)
+v = torch.randn(total, 2, 256, device="cuda", dtype=torch.bfloat16)
+out, lse = zigfa.flash_attn_varlen_func(q, k, v, cu, cu, 513, 513, causal=True, return_attn_probs=True)
+results["varlen"] = (out.cpu(), lse.cpu())
+torch.save(results, sys.argv[2])
+"""
+
+
+def test_head_dim_256_two_cta_variant_matches_the_single_cta_kernel(tmp_path):
+    """The `cta_group::2` variant of the head_dim 256 forward (selected by B200FA_FWD_D256_PAIR=1 when the library
+    handles its first head_dim 256 call, hence the child processes) computes every tile in the same order as the default
+    kernel: out and lse agree bit for bit on fixed-length, windowed and packed inputs."""
+    import os
+    import subprocess
+    import sys
+
+    package = str(next(path for path in sys.path if os.path.isdir(os.path.join(path, "zigfa"))))
+    outputs = {}
+    for switch in ("0", "1"):
+        target = tmp_path / f"pair{switch}.pt"
+        env = dict(os.environ, B200FA_FWD_D256_PAIR=switch)
+        done = subprocess.run([sys.executable, "-c", PAIR_SCRIPT, package, str(target)], env=env, capture_output=True, text=True, timeout=600)
+        assert done.returncode == 0, done.stderr[-2000:]
+        outputs[switch] = torch.load(target)
+    for name, (out, lse) in outputs["0"].items():
+        out_pair, lse_pair = outputs["1"][name]
+        assert torch.equal(out, out_pair) and torch.equal(lse, lse_pair), name

@@ -17,6 +17,7 @@
 // maximum exceeds it by more than 8 (in log2 units), so O is almost never rescaled (reference
 // zig/flash_fwd_sm100.zig:963-976).
 #include <atomic>
+#include <cstdlib>
 
 #include "fwd_common.cuh"
 
@@ -585,8 +586,15 @@ int launch_fwd(const b200fa_fwd_args& a, cudaStream_t stream) {
     case 96:
     case 128:
       return launch_fwd_d<128>(a, stream);
-    case 256:
-      return launch_fwd_256(a, stream);
+    case 256: {
+      // B200FA_FWD_D256_PAIR=1 in the environment selects the two-CTA variant (same results bit for bit, measured
+      // slower: kept for tuning work on `cta_group::2` tiles).
+      static const bool pair_kernel = [] {
+        const char* value = getenv("B200FA_FWD_D256_PAIR");
+        return value && value[0] == '1';
+      }();
+      return pair_kernel ? launch_fwd_256_pair(a, stream) : launch_fwd_256(a, stream);
+    }
     case 512:
       return launch_fwd_512(a, stream);
     default:

@@ -122,6 +122,7 @@ int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim,
 // memset node ahead of the kernel, so launches on different streams never share one). Defined in fwd.cu.
 int acquire_tile_counter(cudaStream_t stream, int** counter);
 int launch_fwd_256(const b200fa_fwd_args& a, cudaStream_t stream);
+int launch_fwd_256_pair(const b200fa_fwd_args& a, cudaStream_t stream);  // two-CTA variant (fwd_d256_pair.cu)
 int launch_fwd_512(const b200fa_fwd_args& a, cudaStream_t stream);
 
 }  // namespace b200fa

@@ -1,0 +1,516 @@
+// Forward attention kernel for head_dim 256 on sm_100a as a pair of CTAs (cluster of two, tcgen05 `cta_group::2`).
+//
+// The single-CTA kernel of fwd_d256.cu is bound by shared-memory bandwidth (its MMAs read 192 KB of operands per key
+// block and the loads write 128 KB). Here two CTAs share every MMA: the pair owns 256 query rows of one head (rows
+// [0,128) in the leader, rank 0, and [128,256) in its peer), and each CTA keeps only half of the B operands,
+//   S(n)  = Q K_n^T    M = 256, N = 128: each CTA holds its 128 rows of Q and 64 of the 128 keys of K_n (32 KB)
+//   O    += P(n) V_n   M = 256, N = 256: each CTA holds 128 of the 256 columns of V_n (16 KB per 64 keys)
+// so a CTA reads 128 KB and writes 64 KB per key block. The reference builds its head_dim 256 forward as a 2-CTA
+// variant as well (zig/configurations.zig:1567-1574).
+// Roles per CTA as in fwd_d256.cu (warps 0-3 softmax, warp 4 MMA, warp 5 loads); only the leader's warp 4 issues MMAs.
+// Barriers that gate the MMAs live in the leader: the loads of both CTAs complete on the leader's `full` barriers
+// (`cp.async.bulk.tensor ... cta_group::2`, no multicast), and the softmax threads of the peer arrive on the leader's P
+// barriers through the cluster's shared-memory window. Barriers that the MMAs release (scores present, slots empty,
+// PV done) exist in both CTAs and the leader commits to each of them in turn.
+// Work items are assigned statically: pair c takes items c, c + pairs, ...
+#include "fwd_common.cuh"
+
+namespace b200fa {
+
+namespace d256p {
+constexpr int D = 256;
+constexpr int kPairRows = 2 * kBlockM;            // query rows per work item
+constexpr int kVSlots = 4;                        // ring of V half-blocks (64 keys)
+constexpr int kKSlots = 2;                        // K blocks in flight
+constexpr int kQBytes = kBlockM * D * 2;          // 64 KB: this CTA's 128 query rows
+constexpr int kKBytes = 64 * D * 2;               // 32 KB: this CTA's 64 keys of a 128-key block
+constexpr int kVBytes = 64 * 128 * 2;             // 16 KB: 64 keys x this CTA's 128 columns
+constexpr int kQPanel = kBlockM * 128;            // 64-column panel of Q (128 rows)
+constexpr int kKPanel = 64 * 128;                 // 64-column panel of the K half (64 rows)
+constexpr int kVPanel = 64 * 128;                 // 64-column panel of a V half-block (64 rows)
+constexpr int kSmemBytes = kQBytes + kKSlots * kKBytes + kVSlots * kVBytes + 1024 + 512;
+constexpr int kThreads = 256;
+constexpr int kTmemO = 256;
+static_assert(kSmemBytes <= 232448, "shared memory exceeds the per-CTA limit");
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of `addr` (a shared-memory address of this CTA) in CTA `rank` of the cluster, in the shared::cluster window.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  // default semantics (release at CTA scope): what is published is TMEM content, ordered by the tcgen05 fences; a
+  // release at cluster scope costs the arriving warp about 1300 cycles
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA load whose bytes complete on a barrier given as a shared::cluster address (the leader's), no multicast.
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t smem_dst, const void* tmap, uint32_t bar_cluster, int c0, int c1,
+                                                 int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], "
+      "[%2];"
+      :
+      : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Completion of all MMAs issued so far arrives on one barrier (a shared::cluster address: own CTA or the peer).
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory");
+}
+}  // namespace d256p
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(d256p::kThreads, 1)
+fwd_d256_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ FwdParams p) {
+  using namespace d256p;
+  constexpr int NV = kVSlots, NK = kKSlots;
+  extern __shared__ uint8_t smem_raw[];
+  // The dynamic shared memory starts at the same offset in both CTAs, so rounding up gives both the same layout.
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t smem_q = smem_base;
+  const uint32_t smem_k = smem_q + kQBytes;
+  const uint32_t smem_v = smem_k + NK * kKBytes;
+  const uint32_t bars = smem_v + NV * kVBytes;
+  const uint32_t bar_q_full = bars, bar_q_empty = bars + 8;
+  const uint32_t bar_k_full = bars + 16 /*[NK]*/, bar_k_empty = bar_k_full + 8 * NK;
+  const uint32_t bar_v_full = bar_k_empty + 8 * NK /*[NV]*/, bar_v_empty = bar_v_full + 8 * NV;
+  const uint32_t bar_s_full = bar_v_empty + 8 * NV;  // [2]
+  const uint32_t bar_p_half = bar_s_full + 16;       // [2]
+  const uint32_t bar_p_full = bar_p_half + 16;       // [2]
+  const uint32_t bar_pv_done = bar_p_full + 16;
+  const uint32_t tmem_slot = bar_pv_done + 8, abort_slot = tmem_slot + 4;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + (abort_slot - smem_u32(smem_raw)));
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+  const WaitCtx wctx{abort_flag, p.status, p.trace};
+  int trace_n = 0;  // timeline of the first work item of pair 0 (tuning builds)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    // full barriers: one arrival (the leader's expect_tx) plus the bytes of both CTAs; used in the leader only
+    mbar_init(bar_q_full, 1);
+    mbar_init(bar_q_empty, 1);
+    for (int i = 0; i < NK; ++i) {
+      mbar_init(bar_k_full + 8 * i, 1);
+      mbar_init(bar_k_empty + 8 * i, 1);
+    }
+    for (int i = 0; i < NV; ++i) {
+      mbar_init(bar_v_full + 8 * i, 1);
+      mbar_init(bar_v_empty + 8 * i, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_s_full + 8 * i, 1);
+      mbar_init(bar_p_half + 8 * i, 8);  // one arrival per softmax warp of both CTAs (leader's copy only)
+      mbar_init(bar_p_full + 8 * i, 8);
+    }
+    mbar_init(bar_pv_done, 1);
+    fence_barrier_init();
+  }
+  if (warp == 4) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // barriers and TMEM of both CTAs exist before anything crosses between them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+  const Problem& pr = p.prob;
+  const int pairs = gridDim.x >> 1, pair = blockIdx.x >> 1;
+
+  auto count_blocks = [&](const FwdTile& t) {
+    KeyCursor cur;
+    cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kPairRows, t.s.lq));
+    OtherBlock kb;
+    int n = 0;
+    while (cur.next(&kb)) ++n;
+    return n;
+  };
+
+  if (warp == 5) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs, own halves)
+    // Load order = consumption order of the MMA warp: K0, K1, then V_hi(n), V_lo(n), K(n + 2) for n = 0, 1, ...
+    if (lane == 0) {
+      uint32_t k_count = 0, v_count = 0, q_count = 0;
+      bool ok = true;
+      const uint32_t lead_q_full = map_to_rank(bar_q_full, 0);
+      auto load_k = [&](int head, int row, int batch_coord) -> bool {  // this CTA's 64 keys of the block at `row`
+        const uint32_t slot = k_count % NK, phase = (k_count / NK) & 1;
+        if (!mbar_wait(bar_k_empty + 8 * slot, phase ^ 1, wctx, kWaitKvEmpty)) return false;
+        if (leader) mbar_expect_tx(bar_k_full + 8 * slot, 2 * kKBytes);
+        const uint32_t bar = map_to_rank(bar_k_full + 8 * slot, 0);
+#pragma unroll
+        for (int h = 0; h < 4; ++h)
+          tma_load_4d_pair(smem_k + slot * kKBytes + h * kKPanel, &map_k, bar, h * 64, head, row + 64 * (int)rank, batch_coord);
+        ++k_count;
+        return true;
+      };
+      auto load_v_half = [&](int head, int row, int batch_coord) -> bool {  // 64 keys at `row`, this CTA's 128 columns
+        const uint32_t slot = v_count % NV, phase = (v_count / NV) & 1;
+        if (!mbar_wait(bar_v_empty + 8 * slot, phase ^ 1, wctx, kWaitKvEmpty)) return false;
+        if (leader) mbar_expect_tx(bar_v_full + 8 * slot, 2 * kVBytes);
+        const uint32_t bar = map_to_rank(bar_v_full + 8 * slot, 0);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          tma_load_4d_pair(smem_v + slot * kVBytes + h * kVPanel, &map_v, bar, 128 * (int)rank + h * 64, head, row, batch_coord);
+        ++v_count;
+        return true;
+      };
+      for (int tile = pair; ok && tile < p.num_tiles; tile += pairs) {
+        FwdTile t = decode_tile(p, tile, kPairRows);
+        if (!t.valid) continue;
+        const int n_blocks = count_blocks(t);
+        if (n_blocks == 0) continue;
+        KeyCursor cur_k, cur_v;
+        cur_k.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kPairRows, t.s.lq));
+        cur_v.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kPairRows, t.s.lq));
+        OtherBlock kb;
+        if (!mbar_wait(bar_q_empty, (q_count & 1) ^ 1, wctx, kWaitQEmpty)) { ok = false; break; }
+        ++q_count;
+        if (leader) mbar_expect_tx(bar_q_full, 2 * kQBytes);
+#pragma unroll
+        for (int h = 0; h < 4; ++h)
+          tma_load_4d_pair(smem_q + h * kQPanel, &map_q, lead_q_full, h * 64, t.head, t.s.q0 + t.m0 + kBlockM * (int)rank,
+                           t.s.batch_coord);
+        for (int i = 0; ok && i < imin(2, n_blocks); ++i) {
+          cur_k.next(&kb);
+          ok = load_k(t.kv_head, kb.row, t.s.batch_coord);
+        }
+        for (int n = 0; ok && n < n_blocks; ++n) {
+          cur_v.next(&kb);
+          ok = load_v_half(t.kv_head, kb.row + 64, t.s.batch_coord) && load_v_half(t.kv_head, kb.row, t.s.batch_coord);
+          if (ok && n + 2 < n_blocks) {
+            cur_k.next(&kb);
+            ok = load_k(t.kv_head, kb.row, t.s.batch_coord);
+          }
+        }
+      }
+    }
+  } else if (warp == 4) {
+    // ------------------------------------------------------------------ MMA issuer (leader) / last-commit watcher (peer)
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(kPairRows, kBlockN, 0, 0);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(kPairRows, D, 0, 1);
+      uint32_t k_count = 0, v_count = 0, q_count = 0;
+      uint32_t p_phase[2] = {0, 0};
+      bool ok = true;
+      // Every barrier that the MMAs release exists in both CTAs: the peer's copy first, then this CTA's.
+      auto commit_both = [&](uint32_t bar) {
+        tc_commit_pair(map_to_rank(bar, 1));
+        tc_commit_pair(map_to_rank(bar, 0));
+      };
+      // S = Q K^T into score buffer `buffer` of both CTAs.
+      auto issue_s = [&](int buffer) -> bool {
+        const uint32_t slot = k_count % NK, phase = (k_count / NK) & 1;
+        if (!mbar_wait(bar_k_full + 8 * slot, phase, wctx, kWaitKvFull)) return false;
+        trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 200 + (k_count % 100));  // K present
+        ++k_count;
+        tc_fence_after();
+        const uint32_t k_smem = smem_k + slot * kKBytes;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          umma_ss_pair(tmem_base + buffer * 128, umma_smem_desc(smem_q + (kk >> 2) * kQPanel + (kk & 3) * 32, 16, 1024),
+                       umma_smem_desc(k_smem + (kk >> 2) * kKPanel + (kk & 3) * 32, 16, 1024), idesc_s, kk > 0);
+        }
+        commit_both(bar_k_empty + 8 * slot);
+        commit_both(bar_s_full + 8 * buffer);
+        trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 100 + ((k_count - 1) % 100));  // S issued
+        return true;
+      };
+      // O += P[:, 64 h .. 64 h + 64) V_half: the next V slot of the ring holds those 64 keys (128 columns per CTA).
+      auto issue_pv_half = [&](int buffer, int half, bool accumulate) -> bool {
+        const uint32_t slot = v_count % NV, phase = (v_count / NV) & 1;
+        if (!mbar_wait(bar_v_full + 8 * slot, phase, wctx, kWaitKvFull)) return false;
+        ++v_count;
+        tc_fence_after();
+        const uint32_t v_smem = smem_v + slot * kVBytes;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          umma_ts_pair(tmem_base + kTmemO, tmem_base + buffer * 128 + 64 + (4 * half + kk) * 8,
+                       umma_smem_desc(v_smem + kk * 2048, kVPanel, 1024), idesc_pv, accumulate || kk > 0);
+        }
+        commit_both(bar_v_empty + 8 * slot);
+        return true;
+      };
+      for (int tile = pair; ok && tile < p.num_tiles; tile += pairs) {
+        FwdTile t = decode_tile(p, tile, kPairRows);
+        if (!t.valid) continue;
+        const int n_blocks = count_blocks(t);
+        if (n_blocks == 0) continue;
+        const uint32_t q_phase = q_count & 1;
+        ++q_count;
+        if (!mbar_wait(bar_q_full, q_phase, wctx, kWaitQFull)) { ok = false; break; }
+        for (int i = 0; ok && i < imin(2, n_blocks); ++i) ok = issue_s(i);
+        for (int n = 0; ok && n < n_blocks; ++n) {
+          const int buffer = n & 1;
+          // keys [64,128) first: their probabilities are stored first
+          if (!mbar_wait(bar_p_half + 8 * buffer, p_phase[buffer], wctx, kWaitPFull)) { ok = false; break; }
+          trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 300 + (n % 100));  // first half of P present
+          if (!issue_pv_half(buffer, 1, n > 0)) { ok = false; break; }
+          trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 400 + (n % 100));  // PV of the first half issued
+          if (!mbar_wait(bar_p_full + 8 * buffer, p_phase[buffer], wctx, kWaitPFull)) { ok = false; break; }
+          trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 500 + (n % 100));  // all of P present
+          p_phase[buffer] ^= 1;
+          if (!issue_pv_half(buffer, 0, true)) { ok = false; break; }
+          commit_both(bar_pv_done);
+          trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 600 + (n % 100));  // PV of the second half issued
+          if (n + 2 < n_blocks) ok = issue_s(buffer);
+        }
+        if (ok) commit_both(bar_q_empty);
+      }
+      if (ok && q_count > 0) mbar_wait(bar_q_empty, (q_count - 1) & 1, wctx, kWaitQEmpty);
+    } else if (lane == 0) {
+      // The peer must not leave before the last commit of the leader has arrived on its barriers.
+      uint32_t q_count = 0;
+      for (int tile = pair; tile < p.num_tiles; tile += pairs) {
+        FwdTile t = decode_tile(p, tile, kPairRows);
+        if (t.valid && count_blocks(t) > 0) ++q_count;
+      }
+      for (uint32_t i = 0; i < q_count; ++i)
+        if (!mbar_wait(bar_q_empty, i & 1, wctx, kWaitQEmpty)) break;
+    }
+  } else if (warp < 4) {
+    // ------------------------------------------------------------------ softmax + epilogue (thread = query row)
+    const int row_in_tile = warp * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t t_o = tmem_base + lane_addr + kTmemO;
+    const float scale_log2 = p.scale_log2;
+    uint32_t blocks = 0;
+    // P barriers of the leader as seen from this CTA
+    const uint32_t lead_p_half = map_to_rank(bar_p_half, 0), lead_p_full = map_to_rank(bar_p_full, 0);
+    uint32_t s_phase[2] = {0, 0};
+    bool ok = true;
+    for (int tile = pair; ok && tile < p.num_tiles; tile += pairs) {
+      FwdTile t = decode_tile(p, tile, kPairRows);
+      if (!t.valid) continue;
+      const int row = t.m0 + kBlockM * (int)rank + row_in_tile;
+      KeyCursor cur;
+      cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kPairRows, t.s.lq));
+      const int band_lo = cur.band.lo(row), band_hi = cur.band.hi(row);
+      float m = -INFINITY, l = 0.f;
+      int tile_blocks = 0;
+      OtherBlock kb;
+      while (cur.next(&kb)) {
+        const int buffer = tile_blocks & 1;
+        const uint32_t t_s = tmem_base + lane_addr + buffer * 128;
+        if (!mbar_wait_warp(bar_s_full + 8 * buffer, s_phase[buffer], wctx, kWaitSFull)) { ok = false; break; }
+        s_phase[buffer] ^= 1;
+        tc_fence_after();
+        const bool traced = blockIdx.x < 2 && threadIdx.x == 0 && tile == pair;
+        const int trole = 1 + (int)rank;
+        trace_event(wctx, traced, trole, trace_n, 2000 + 1000 * (int)rank + (tile_blocks % 100));  // scores present
+        int lo, hi;
+        if (kb.banded) {
+          lo = band_lo - kb.col0;
+          hi = band_hi - kb.col0;
+        } else {
+          lo = 0;
+          hi = kb.limit - kb.col0;
+        }
+        const bool masked = __any_sync(0xffffffffu, lo > 0 || hi < kBlockN);
+        auto apply_mask = [&](float2* values, int first_column) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int c = first_column + 2 * i;
+            values[i].x = (c >= lo && c < hi) ? values[i].x : -INFINITY;
+            values[i].y = (c + 1 >= lo && c + 1 < hi) ? values[i].y : -INFINITY;
+          }
+        };
+        auto max_of = [&](const float2* values) {
+          float a = fmaxf(values[0].x, values[0].y), b = fmaxf(values[1].x, values[1].y);
+          float c = fmaxf(values[2].x, values[2].y), d = fmaxf(values[3].x, values[3].y);
+#pragma unroll
+          for (int i = 4; i < 32; i += 4) {
+            a = fmaxf(a, fmaxf(values[i].x, values[i].y));
+            b = fmaxf(b, fmaxf(values[i + 1].x, values[i + 1].y));
+            c = fmaxf(c, fmaxf(values[i + 2].x, values[i + 2].y));
+            d = fmaxf(d, fmaxf(values[i + 3].x, values[i + 3].y));
+          }
+          return fmaxf(fmaxf(a, b), fmaxf(c, d));
+        };
+        // Pass 1: row maximum. Columns [0,64) are read for the maximum only and read again in pass 2; columns
+        // [64,128) stay in registers, because P goes over them.
+        float2 low[32], high[32];
+        tmem_ld32(t_s, reinterpret_cast<uint32_t*>(low));
+        tmem_ld32(t_s + 32, reinterpret_cast<uint32_t*>(low) + 32);
+        tc_wait_ld();
+        trace_event(wctx, traced, trole, trace_n, 4000 + 1000 * (int)rank + (tile_blocks % 100));  // lower scores in registers
+        if (masked) apply_mask(low, 0);
+        const float max_low = max_of(low);
+        tmem_ld32(t_s + 64, reinterpret_cast<uint32_t*>(high));
+        tmem_ld32(t_s + 96, reinterpret_cast<uint32_t*>(high) + 32);
+        tc_wait_ld();
+        if (masked) apply_mask(high, 64);
+        const float m_new = fmaxf(m, fmaxf(max_low, max_of(high)));
+        trace_event(wctx, traced, trole, trace_n, 6000 + 1000 * (int)rank + (tile_blocks % 100));  // row maximum known
+        const bool grow = (m_new - m) * scale_log2 > 8.f;  // also true when m is -inf and m_new is finite
+        if (__any_sync(0xffffffffu, grow)) {
+          float alpha = 1.f;
+          if (grow) {
+            alpha = (m == -INFINITY) ? 0.f : ex2_approx((m - m_new) * scale_log2);
+            l *= alpha;
+            m = m_new;
+          }
+          if (tile_blocks > 0) {
+            if (!mbar_wait_warp(bar_pv_done, (blocks - 1) & 1, wctx, kWaitPvDone)) { ok = false; break; }
+            tc_fence_after();
+            const float2 alpha2 = make_float2(alpha, alpha);
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              float2 o[16];
+              tmem_ld32(t_o + 32 * c, reinterpret_cast<uint32_t*>(o));
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) o[i] = __fmul2_rn(o[i], alpha2);
+              tmem_st32(t_o + 32 * c, reinterpret_cast<uint32_t*>(o));
+            }
+          }
+        }
+        const float mc = (m == -INFINITY) ? 0.f : m * scale_log2;
+        const float2 scale2 = make_float2(scale_log2, scale_log2), shift2 = make_float2(-mc, -mc);
+        float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
+        // 64 scores -> 64 probabilities (BF16) stored at P columns [first_p_column, first_p_column + 32)
+        auto exponentiate = [&](const float2* values, uint32_t first_p_column) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            uint32_t packed[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float2 x = __ffma2_rn(values[16 * c + i], scale2, shift2);
+              float2 e;
+              e.x = ex2_approx(x.x);
+              e.y = ex2_approx(x.y);
+              if (i & 1) sum_b = __fadd2_rn(sum_b, e); else sum_a = __fadd2_rn(sum_a, e);
+              packed[i] = pack_bf16x2(e.x, e.y);
+            }
+            tmem_st16(t_s + 64 + first_p_column + 16 * c, packed);
+          }
+        };
+        // Pass 2 for columns [0,64): the loads are in flight while the upper half is exponentiated.
+        tmem_ld32(t_s, reinterpret_cast<uint32_t*>(low));
+        tmem_ld32(t_s + 32, reinterpret_cast<uint32_t*>(low) + 32);
+        exponentiate(high, 32);
+        trace_event(wctx, traced, trole, trace_n, 8000 + 1000 * (int)rank + (tile_blocks % 100));  // upper half exponentiated
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(lead_p_half + 8 * buffer);  // keys [64,128): their half of the PV product may start
+        trace_event(wctx, traced, trole, trace_n, 2200 + 1000 * (int)rank + (tile_blocks % 100));  // first half of P stored
+        tc_wait_ld();
+        if (masked) apply_mask(low, 0);
+        exponentiate(low, 0);
+        l += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
+        // Observe the PV product of the previous block before releasing this one: the scores of block n only prove that
+        // PV(n - 2) has completed, and a parity wait cannot tell a barrier that is two completions behind from one that
+        // is done.
+        if (tile_blocks > 0 && !mbar_wait_warp(bar_pv_done, (blocks - 1) & 1, wctx, kWaitPvDone)) { ok = false; break; }
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(lead_p_full + 8 * buffer);
+        trace_event(wctx, traced, trole, trace_n, 2400 + 1000 * (int)rank + (tile_blocks % 100));  // all of P stored
+        ++blocks;
+        ++tile_blocks;
+      }
+      if (!ok) break;
+      // ---- epilogue
+      const bool row_valid = row < t.s.lq;
+      __nv_bfloat16* o_row = p.o + t.s.batch_coord * p.o_batch_stride + (int64_t)(t.s.q0 + row) * p.o_row_stride +
+                             (int64_t)t.head * p.o_head_stride;
+      float* lse_ptr = p.lse + t.s.batch_coord * p.lse_batch_stride + (int64_t)t.head * p.lse_head_stride + t.s.q0 + row;
+      if (tile_blocks == 0) {
+        if (row_valid) {
+          const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll
+          for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(o_row)[c] = zero;
+          *lse_ptr = -INFINITY;
+        }
+        continue;
+      }
+      if (!mbar_wait_warp(bar_pv_done, (blocks - 1) & 1, wctx, kWaitEpilogue)) { ok = false; break; }
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(t_o + 32 * c, o);
+        tc_wait_ld();
+        if (row_valid) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(o[8 * i + 0]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
+            v.y = pack_bf16x2(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
+            v.z = pack_bf16x2(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
+            v.w = pack_bf16x2(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
+            reinterpret_cast<uint4*>(o_row)[4 * c + i] = v;
+          }
+        }
+      }
+      if (row_valid) {
+        const float mc = (m == -INFINITY) ? 0.f : m * scale_log2;
+        *lse_ptr = l > 0.f ? (mc + log2f(l)) * 0.69314718055994531f : -INFINITY;
+      }
+      tc_fence_before();
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (*abort_flag) {
+    for (int i = 0; i < 50; ++i) __nanosleep(20000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the leader's MMAs read the peer's shared memory and write its TMEM until here
+  tc_fence_after();
+  if (warp == 4) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+}
+
+int launch_fwd_256_pair(const b200fa_fwd_args& a, cudaStream_t stream) {
+  FwdParams p;
+  CUtensorMap map_q, map_k, map_v;
+  bool nothing_to_do = false;
+  int status = prepare_forward(a, stream, d256p::D, d256p::kPairRows, 64, &p, &map_q, &map_k, &map_v, &nothing_to_do, 64);
+  if (status != B200FA_OK || nothing_to_do) return status;
+  static bool attribute_set[64] = {false};
+  status = set_dynamic_smem_once(reinterpret_cast<const void*>(&fwd_d256_pair_kernel), d256p::kSmemBytes, attribute_set);
+  if (status != B200FA_OK) return status;
+  int sms = 0;
+  status = device_sm_count(&sms);
+  if (status != B200FA_OK) return status;
+  const int pairs = p.num_tiles < sms / 2 ? p.num_tiles : sms / 2;
+  fwd_d256_pair_kernel<<<2 * pairs, d256p::kThreads, d256p::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+  B200FA_CUDA_CHECK(cudaGetLastError());
+  return B200FA_OK;
+}
+
+}  // namespace b200fa

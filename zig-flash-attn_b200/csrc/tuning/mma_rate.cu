@@ -15,11 +15,17 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity) {
 
 template <int N, int MODE>  // MODE 0: SS, both operands K-major, one accumulator; 1: the same with two accumulators in turn; 2: TS (A in TMEM);
                              // 3: SS with B MN-major; 4: SS with A and B MN-major
-__global__ void __launch_bounds__(128, 1) rate_kernel(long long* out, int count) {
+__global__ void __launch_bounds__(128, 1) rate_kernel(long long* out, int count, int fill) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t base = smem_u32(smem);
   const uint32_t bar = base + 200 * 1024, slot = bar + 16;
-  for (int i = threadIdx.x; i < 200 * 1024 / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(smem)[i] = 0;
+  // Operands: zeros, or (fill != 0) BF16 values in (-2, -1] and [1, 2) with random mantissas, which toggle the datapath
+  // the way real data does (the MMA rate under load depends on it).
+  for (int i = threadIdx.x; i < 200 * 1024 / 4; i += blockDim.x) {
+    uint32_t h = (i + 1) * 2654435761u + blockIdx.x * 40503u;
+    h ^= h >> 15; h *= 2246822519u; h ^= h >> 13;
+    reinterpret_cast<uint32_t*>(smem)[i] = fill ? ((h & 0x807f807fu) | 0x3f803f80u) : 0u;
+  }
   if (threadIdx.x == 0) { mbar_init(bar, 1); fence_barrier_init(); }
   if (threadIdx.x < 32) { tmem_alloc(slot, 512); tmem_relinquish(); }
   fence_proxy_async_smem();
@@ -55,14 +61,14 @@ __global__ void __launch_bounds__(128, 1) rate_kernel(long long* out, int count)
 }
 
 template <int N, int MODE>
-void run(const char* name, int ctas, int count) {
+void run(const char* name, int ctas, int count, int fill = 0) {
   long long* out; cudaMalloc(&out, 128); cudaMemset(out, 0, 128);
   const int smem = 200 * 1024 + 64;
   cudaFuncSetAttribute(rate_kernel<N, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  rate_kernel<N, MODE><<<ctas, 128, smem>>>(out, count);
+  rate_kernel<N, MODE><<<ctas, 128, smem>>>(out, count, fill);
   cudaError_t e = cudaDeviceSynchronize();
   long long h[9]; cudaMemcpy(h, out, sizeof(h), cudaMemcpyDeviceToHost);
-  printf("%-34s ctas %3d: issue %6.1f  total %6.1f cycles per MMA (ok %lld) %s\n", name, ctas, double(h[6]) / count, double(h[7]) / count,
+  printf("%-34s %s ctas %3d: issue %6.1f  total %6.1f cycles per MMA (ok %lld) %s\n", name, fill ? "random" : "zeros ", ctas, double(h[6]) / count, double(h[7]) / count,
          h[8], e == cudaSuccess ? "" : cudaGetErrorString(e));
   cudaFree(out);
 }
@@ -83,6 +89,13 @@ int main() {
     run<256, 3>("SS N=256 B MN-major", ctas, count);
     run<64, 4>("SS N=64 A and B MN-major", ctas, count);
     run<128, 4>("SS N=128 A and B MN-major", ctas, count);
+  }
+  // The same instructions on random operands, long enough for the power management to react (each run about 40 ms).
+  for (int ctas : {1, 148}) {
+    run<128, 0>("SS N=128 one accumulator", ctas, 1 << 20, 1);
+    run<256, 0>("SS N=256 one accumulator", ctas, 1 << 19, 1);
+    run<128, 3>("SS N=128 B MN-major", ctas, 1 << 20, 1);
+    run<128, 0>("SS N=128 one accumulator", ctas, 1 << 20, 0);
   }
   return 0;
 }
