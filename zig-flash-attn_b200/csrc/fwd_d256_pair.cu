@@ -9,7 +9,7 @@
 // variant as well (zig/configurations.zig:1567-1574).
 // Roles per CTA as in fwd_d256.cu (warps 0-3 softmax, warp 4 MMA, warp 5 loads); only the leader's warp 4 issues MMAs.
 // Barriers that gate the MMAs live in the leader: the loads of both CTAs complete on the leader's `full` barriers
-// (`cp.async.bulk.tensor ... cta_group::2`, no multicast), and the softmax threads of the peer arrive on the leader's P
+// (each CTA's own TMA loads in their `cta_group::2` form), and the softmax threads of the peer arrive on the leader's P
 // barriers through the cluster's shared-memory window. Barriers that the MMAs release (scores present, slots empty,
 // PV done) exist in both CTAs and the leader commits to each of them in turn.
 // Work items are assigned statically: pair c takes items c, c + pairs, ...
@@ -52,7 +52,8 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// TMA load whose bytes complete on a barrier given as a shared::cluster address (the leader's), no multicast.
+// TMA load into this CTA's shared memory whose bytes complete on a barrier given as a shared::cluster address (the
+// leader's).
 __device__ __forceinline__ void tma_load_4d_pair(uint32_t smem_dst, const void* tmap, uint32_t bar_cluster, int c0, int c1,
                                                  int c2, int c3) {
   asm volatile(
