@@ -8,6 +8,14 @@
 #include "../ptx.cuh"
 using namespace b200fa;
 
+__device__ __forceinline__ float4 ld_shared_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity) {
   for (int i = 0; i < 4000000; ++i) if (mbar_try_wait(bar, parity)) return true;
   return false;
@@ -15,7 +23,7 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity) {
 
 template <int N, int MODE>  // MODE 0: SS, both operands K-major, one accumulator; 1: the same with two accumulators in turn; 2: TS (A in TMEM);
                              // 3: SS with B MN-major; 4: SS with A and B MN-major
-__global__ void __launch_bounds__(128, 1) rate_kernel(long long* out, int count, int fill) {
+__global__ void __launch_bounds__(384, 1) rate_kernel(long long* out, int count, int fill, int load) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t base = smem_u32(smem);
   const uint32_t bar = base + 200 * 1024, slot = bar + 16;
@@ -33,6 +41,35 @@ __global__ void __launch_bounds__(128, 1) rate_kernel(long long* out, int count,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(smem + 200 * 1024 + 16);
+  volatile int* stop = reinterpret_cast<volatile int*>(smem + 200 * 1024 + 32);
+  if (threadIdx.x == 0) *stop = 0;
+  __syncthreads();
+  if (threadIdx.x >= 128 && load != 0) {
+    // Background work of the kind the attention kernels run next to their MMAs, on warps 4-11 until thread 0 is done:
+    // load 1 = exp2 and FMA arithmetic, 2 = TMEM loads and stores (columns 384-511), 3 = shared-memory copies.
+    float x = 0.001f * threadIdx.x, y = 1.f;
+    uint32_t regs[32];
+    for (int i = 0; i < 32; ++i) regs[i] = threadIdx.x + i;
+    const uint32_t taddr = tmem + (static_cast<uint32_t>((threadIdx.x >> 5) & 3) * 32 << 16) + 384 + 32 * (((threadIdx.x >> 7) - 1) & 1);
+    const uint32_t saddr = base + 128 * 1024 + (threadIdx.x - 128) * 16;
+    while (!*stop) {
+      for (int it = 0; it < 64; ++it) {
+        if (load == 1) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { x = ex2_approx(-x * 0.5f); y = fmaf(y, 0.999f, x); }
+        } else if (load == 2) {
+          tmem_ld32(taddr, regs);
+          tc_wait_ld();
+          tmem_st32(taddr, regs);
+          tc_wait_st();
+        } else {
+          float4 v = ld_shared_f4(saddr + (it & 15) * 4096);
+          st_shared_v4(saddr + 65536 - 4096 * (it & 7), __float_as_uint(v.x), __float_as_uint(v.y), __float_as_uint(v.z), __float_as_uint(v.w));
+        }
+      }
+    }
+    if (x + y == 12345.f && regs[3] == 77) out[15] = 1;
+  }
   if (threadIdx.x == 0) {
     constexpr uint32_t idesc = umma_idesc_bf16(128, N, MODE == 4 ? 1 : 0, MODE >= 3 ? 1 : 0);
     const uint32_t a = base, b = base + 64 * 1024;
@@ -53,6 +90,7 @@ __global__ void __launch_bounds__(128, 1) rate_kernel(long long* out, int count,
       if (blockIdx.x == 0) { out[3 * rep] = t1 - t0; out[3 * rep + 1] = t2 - t0; out[3 * rep + 2] = ok; }
       if (!ok) break;
     }
+    *stop = 1;
   }
   tc_fence_before();
   __syncthreads();
@@ -61,14 +99,14 @@ __global__ void __launch_bounds__(128, 1) rate_kernel(long long* out, int count,
 }
 
 template <int N, int MODE>
-void run(const char* name, int ctas, int count, int fill = 0) {
+void run(const char* name, int ctas, int count, int fill = 0, int load = 0) {
   long long* out; cudaMalloc(&out, 128); cudaMemset(out, 0, 128);
   const int smem = 200 * 1024 + 64;
   cudaFuncSetAttribute(rate_kernel<N, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  rate_kernel<N, MODE><<<ctas, 128, smem>>>(out, count, fill);
+  rate_kernel<N, MODE><<<ctas, 384, smem>>>(out, count, fill, load);
   cudaError_t e = cudaDeviceSynchronize();
   long long h[9]; cudaMemcpy(h, out, sizeof(h), cudaMemcpyDeviceToHost);
-  printf("%-34s %s ctas %3d: issue %6.1f  total %6.1f cycles per MMA (ok %lld) %s\n", name, fill ? "random" : "zeros ", ctas, double(h[6]) / count, double(h[7]) / count,
+  printf("%-34s %s ctas %3d: issue %6.1f  total %6.1f cycles per MMA (ok %lld) %s\n", name, load == 0 ? (fill ? "random" : "zeros ") : load == 1 ? "rnd+alu" : load == 2 ? "rnd+tmem" : "rnd+smem", ctas, double(h[6]) / count, double(h[7]) / count,
          h[8], e == cudaSuccess ? "" : cudaGetErrorString(e));
   cudaFree(out);
 }
@@ -96,6 +134,10 @@ int main() {
     run<256, 0>("SS N=256 one accumulator", ctas, 1 << 19, 1);
     run<128, 3>("SS N=128 B MN-major", ctas, 1 << 20, 1);
     run<128, 0>("SS N=128 one accumulator", ctas, 1 << 20, 0);
+    for (int load = 1; load <= 3; ++load) {
+      run<128, 0>("SS N=128 one accumulator", ctas, 1 << 18, 1, load);
+      run<256, 0>("SS N=256 one accumulator", ctas, 1 << 17, 1, load);
+    }
   }
   return 0;
 }
