@@ -79,6 +79,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   volatile uint32_t* tmem_ptr_smem =
       reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
   const WaitCtx wctx{abort_flag, p.status, p.trace};
+  int trace_n = 0;  // timeline of the first work item of CTA 0 (tuning builds; see trace_event)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -189,10 +190,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         if (kSplitPv) {
           if (!mbar_wait(bar_p_half + 8 * stage, phase, wctx, kWaitPFull)) return false;
           tc_fence_after();
+          trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 300 + 1000 * stage + (blocks % 100));  // first half of P present
           issue_pv_steps(stage, v_smem, kSteps / 2, kSteps / 2, accumulate);
         }
         if (!mbar_wait_traced(bar_p_full + 8 * stage, phase, wctx, kWaitPFull, 17 + stage, false)) return false;
         tc_fence_after();
+        trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 500 + 1000 * stage + (blocks % 100));  // all of P present
         if (kSplitPv) {
           issue_pv_steps(stage, v_smem, 0, kSteps / 2, true);
         } else {
@@ -236,17 +239,24 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           const uint32_t k_smem = smem_kv + (k_index % NS) * Cfg::kTileBytes;
           const uint32_t phase = blocks & 1;
           if (!issue_pv(0, v_smem, !first, phase)) { ok = false; break; }
-          tc_commit(bar_pv_done);
+          // PV done is announced for the last block of a tile only (the epilogue waits for it). In between, the scores of
+          // block j + 1 being present already proves PV(j) complete: a commit covers every MMA issued before it, and a
+          // tcgen05.commit costs a 128 x 128 x 16 MMA stream about 90 cycles.
+          if (!more) tc_commit(bar_pv_done);
+          trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 600 + (blocks % 100));  // PV of stage 0 issued
           if (more) {
             issue_s(0, k_smem);
             tc_commit(bar_s_full);
+            trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 100 + (blocks % 100));  // S of stage 0 issued
           }
           if (!issue_pv(1, v_smem, !first, phase)) { ok = false; break; }
-          tc_commit(bar_pv_done + 8);
+          if (!more) tc_commit(bar_pv_done + 8);
+          trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 1600 + (blocks % 100));  // PV of stage 1 issued
           tc_commit(bar_kv_empty + 8 * (v_index % NS));
           if (more) {
             issue_s(1, k_smem);
             tc_commit(bar_s_full + 8);
+            trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 1100 + (blocks % 100));  // S of stage 1 issued
             tc_commit(bar_kv_empty + 8 * (k_index % NS));
           } else {
             tc_commit(bar_q_empty);
@@ -272,7 +282,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     const uint32_t my_p_full = bar_p_full + 8 * stage;
     const uint32_t my_pv_done = bar_pv_done + 8 * stage;
     const float scale_log2 = p.scale_log2;
-    uint32_t blocks = 0;
+    uint32_t blocks = 0, tiles_done = 0;  // key blocks and work items with key blocks so far
     bool ok = true;
     uint32_t popped = 0;
     for (int tile; ok && (tile = tiles.pop_warp(popped, wctx)) >= 0;) {
@@ -289,6 +299,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         if (!mbar_wait_traced(my_s_full, blocks & 1, wctx, kWaitSFull, 19, true)) { ok = false; break; }
         const long long t_soft = trace_clock(wctx);
         tc_fence_after();
+        const bool traced = blockIdx.x == 0 && (threadIdx.x & 127) == 0 && popped == 1;
+        trace_event(wctx, traced, 1 + stage, trace_n, 2000 + 1000 * stage + (tile_blocks % 100));  // scores present
         // Column limits of this row inside the block; `masked` is uniform over the warp.
         int lo, hi;
         if (kb.banded) {
@@ -333,6 +345,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         tc_wait_ld();
         if (masked) apply_mask(high, 64);
         const float m_new = fmaxf(m, fmaxf(max_low, max_of(high)));
+        trace_event(wctx, traced, 1 + stage, trace_n, 4000 + 1000 * stage + (tile_blocks % 100));  // row maximum known
         const bool grow = (m_new - m) * scale_log2 > 8.f;  // also true when m is -inf and m_new is finite
         if (__any_sync(0xffffffffu, grow)) {
           float alpha = 1.f;
@@ -342,8 +355,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             m = m_new;
           }
           if (tile_blocks > 0) {
-            if (!mbar_wait_warp(my_pv_done, (blocks - 1) & 1, wctx, kWaitPvDone)) { ok = false; break; }
-            tc_fence_after();
+            // The scores of this block are present, so the PV product of the previous block has completed.
             const float2 alpha2 = make_float2(alpha, alpha);
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
@@ -393,6 +405,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             tc_fence_before();
             mbar_arrive(bar_p_half + 8 * stage);
           }
+          trace_event(wctx, traced, 1 + stage, trace_n, 6000 + 1000 * stage + (tile_blocks % 100));  // first half of P stored
           tc_wait_ld();
           if (masked) apply_mask(low, 0);
           exponentiate(low, 0);
@@ -401,6 +414,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(my_p_full);
+        trace_event(wctx, traced, 1 + stage, trace_n, 8000 + 1000 * stage + (tile_blocks % 100));  // all of P stored
         trace_add(wctx, 20, trace_clock(wctx) - t_soft);
         trace_add(wctx, 21, 1);
         ++blocks;
@@ -422,7 +436,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         }
         continue;
       }
-      if (!mbar_wait_traced(my_pv_done, (blocks - 1) & 1, wctx, kWaitEpilogue, 22, true)) { ok = false; break; }
+      if (!mbar_wait_traced(my_pv_done, tiles_done & 1, wctx, kWaitEpilogue, 22, true)) { ok = false; break; }
+      ++tiles_done;
       const long long t_epi = trace_clock(wctx);
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;

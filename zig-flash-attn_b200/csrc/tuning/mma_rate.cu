@@ -22,7 +22,7 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity) {
 }
 
 template <int N, int MODE>  // MODE 0: SS, both operands K-major, one accumulator; 1: the same with two accumulators in turn; 2: TS (A in TMEM);
-                             // 3: SS with B MN-major; 4: SS with A and B MN-major
+                             // 3: SS with B MN-major; 4: SS with A and B MN-major; 5: as 0 with a tcgen05.commit after every eighth MMA
 __global__ void __launch_bounds__(384, 1) rate_kernel(long long* out, int count, int fill, int load) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t base = smem_u32(smem);
@@ -34,7 +34,7 @@ __global__ void __launch_bounds__(384, 1) rate_kernel(long long* out, int count,
     h ^= h >> 15; h *= 2246822519u; h ^= h >> 13;
     reinterpret_cast<uint32_t*>(smem)[i] = fill ? ((h & 0x807f807fu) | 0x3f803f80u) : 0u;
   }
-  if (threadIdx.x == 0) { mbar_init(bar, 1); fence_barrier_init(); }
+  if (threadIdx.x == 0) { mbar_init(bar, 1); mbar_init(bar + 8, 1 << 20); fence_barrier_init(); }
   if (threadIdx.x < 32) { tmem_alloc(slot, 512); tmem_relinquish(); }
   fence_proxy_async_smem();
   tc_fence_before();
@@ -82,6 +82,7 @@ __global__ void __launch_bounds__(384, 1) rate_kernel(long long* out, int count,
         else if (MODE == 4) umma_ss(d, umma_smem_desc(a + (i & 7) * 2048, 16384, 1024), umma_smem_desc(b + (i & 7) * 2048, 16384, 1024), idesc, i > 1);
         else if (MODE == 3) umma_ss(d, umma_smem_desc(a + off, 16, 1024), umma_smem_desc(b + (i & 7) * 2048, 16384, 1024), idesc, i > 1);
         else umma_ss(d, umma_smem_desc(a + off, 16, 1024), umma_smem_desc(b + off, 16, 1024), idesc, i > 1);
+        if (MODE == 5 && (i & 7) == 7) tc_commit(bar + 8);  // a commit after every eighth MMA, to a barrier nobody waits on
       }
       const long long t1 = clock64();
       tc_commit(bar);
@@ -134,6 +135,8 @@ int main() {
     run<256, 0>("SS N=256 one accumulator", ctas, 1 << 19, 1);
     run<128, 3>("SS N=128 B MN-major", ctas, 1 << 20, 1);
     run<128, 0>("SS N=128 one accumulator", ctas, 1 << 20, 0);
+    run<128, 5>("SS N=128, commit every 8 MMAs", ctas, 1 << 16, 1);
+    run<256, 5>("SS N=256, commit every 8 MMAs", ctas, 1 << 16, 1);
     for (int load = 1; load <= 3; ++load) {
       run<128, 0>("SS N=128 one accumulator", ctas, 1 << 18, 1, load);
       run<256, 0>("SS N=256 one accumulator", ctas, 1 << 17, 1, load);
