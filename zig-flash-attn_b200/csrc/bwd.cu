@@ -107,9 +107,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   const uint32_t smem_lse = base + Cfg::kOffStats, smem_dpsum = smem_lse + 1024;
   const uint32_t bars = base + Cfg::kOffBars;
   const uint32_t bar_kv_full = bars, bar_q_full = bars + 8 /*[2]*/, bar_q_empty = bars + 24 /*[2]*/;
-  const uint32_t bar_do_full = bars + 40, bar_do_empty = bars + 48, bar_s_full = bars + 56, bar_p_full = bars + 64;
+  const uint32_t bar_do_full = bars + 40, bar_s_full = bars + 56, bar_p_full = bars + 64;
   const uint32_t bar_dp_full = bars + 72, bar_ds_full = bars + 80, bar_dq_full = bars + 88, bar_dq_empty = bars + 96;
-  const uint32_t bar_final = bars + 104, bar_ds_empty = bars + 120;
+  const uint32_t bar_final = bars + 104;
   const uint32_t tmem_slot = bars + 112, abort_slot = bars + 116;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + (abort_slot - smem_u32(smem_raw)));
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
@@ -128,7 +128,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     mbar_init(bar_q_empty, 1);
     mbar_init(bar_q_empty + 8, 1);
     mbar_init(bar_do_full, 33);
-    mbar_init(bar_do_empty, 1);
     mbar_init(bar_s_full, 1);
     mbar_init(bar_p_full, 32 * Cfg::kComputeWarps);
     mbar_init(bar_dp_full, 1);
@@ -136,7 +135,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     mbar_init(bar_dq_full, 1);
     mbar_init(bar_dq_empty, 128 * Cfg::kDrains);
     mbar_init(bar_final, 1);
-    mbar_init(bar_ds_empty, 1);
     fence_barrier_init();
   }
   constexpr int kMmaWarp = Cfg::kComputeWarps + 4 * Cfg::kDrains, kLoadWarp = kMmaWarp + 1;
@@ -203,7 +201,12 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           if (row0 + r < p.rows) cp_async_4(smem_lse + st * 512 + r * 4, lse_head + row0 + r);
         }
         cp_async_arrive_noinc(bar_q_full + 8 * st);
-        if (!mbar_wait_traced(bar_do_empty, (it & 1) ^ 1, wctx, kWaitBwdLoad, 1, true)) { ok = false; break; }
+        // The dO tile is free when dV(it - 1) has completed. The commit that announces S^T(it) was issued right after
+        // those MMAs and covers them, so no barrier of its own is spent on it (a tcgen05.commit costs the MMA stream
+        // about 90 cycles).
+        // The wait runs in every iteration, the first included: a parity wait is only valid on a barrier whose earlier
+        // completions the waiter has observed, and completion `it` is that of S^T(it), issued after dV(it - 1).
+        if (!mbar_wait_traced(bar_s_full, it & 1, wctx, kWaitBwdLoad, 1, true)) { ok = false; break; }
         if (lane == 0) {
           trace_event(wctx, traced_cta && it < 10, 3, trace_n, 1000 + it);  // dO load issued
           mbar_expect_tx(bar_do_full, Cfg::kTileBytes);
@@ -262,7 +265,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         for (int kk = 0; kk < 8; ++kk)
           umma_ts(t_dv, t_s + (Cfg::kGroups == 2 ? (kk >> 2) * 64 + (kk & 3) * 8 : (kk >> 1) * 32 + (kk & 1) * 8),
                   umma_smem_desc(smem_do + kk * 2048, Cfg::kPanelBytes, 1024), idesc_dv, it > 0 || kk > 0);
-        tc_commit(bar_do_empty);
         trace_event(wctx, traced_cta && it < 10, 0, trace_n, 100 + it);  // dV issued
         // S^T of the next iteration
         if (more) {
@@ -295,7 +297,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         // dQ first: its drain is on the chain to the next dP^T (same TMEM columns); dK runs while the drain does.
         issue_dq();
         issue_dk();
-        tc_commit(bar_ds_empty);
         trace_event(wctx, traced_cta && it < 10, 0, trace_n, 300 + it);  // dK, dQ issued
         // dP^T of the next iteration (its TMEM columns hold dQ until the reduce warps have drained it)
         if (more) {
@@ -388,7 +389,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         // ---- dS^T = P^T o (dP^T - D), written to shared memory as BF16
         if (!mbar_wait_traced(bar_dp_full, it & 1, wctx, kWaitBwdCompute, 8, true)) { ok = false; break; }
         // The dS tile of the previous iteration must have been consumed by its dK and dQ MMAs.
-        if (it > 0 && !mbar_wait_traced(bar_ds_empty, (it - 1) & 1, wctx, kWaitBwdCompute, 9, true)) { ok = false; break; }
+        if (it > 0 && !mbar_wait_traced(bar_q_empty + 8 * ((it - 1) & 1), ((it - 1) >> 1) & 1, wctx, kWaitBwdCompute, 9, true)) { ok = false; break; }
         tc_fence_after();
         const long long t_ds = trace_clock(wctx);
         trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 700 + it);  // dP ready
