@@ -122,7 +122,7 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t smem_lse = base + kOffStats, smem_dpsum = smem_lse + 512;
   const uint32_t bars = base + kOffBars;
   const uint32_t bar_kv_full = bars, bar_s_full = bars + 8, bar_p_full = bars + 16, bar_dp_full = bars + 24;
-  const uint32_t bar_ds_full = bars + 32, bar_ds_empty = bars + 40, bar_dq_full = bars + 48, bar_dq_empty = bars + 56;
+  const uint32_t bar_ds_full = bars + 32, bar_dq_full = bars + 48, bar_dq_empty = bars + 56;
   const uint32_t bar_final = bars + 64, bar_v_ready = bars + 72;
   const uint32_t bar_q_full = bars + 80 /*[2]*/, bar_q_empty = bars + 96 /*[2]*/, bar_do_full = bars + 112 /*[2]*/;
   const uint32_t bar_do_empty = bars + 128 /*[2]*/;
@@ -148,7 +148,6 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     mbar_init(bar_p_full, 32 * kComputeWarps);
     mbar_init(bar_dp_full, 1);
     mbar_init(bar_ds_full, 32 * kComputeWarps);
-    mbar_init(bar_ds_empty, 1);
     mbar_init(bar_dq_full, 1);
     mbar_init(bar_dq_empty, 128 * kDrains);
     mbar_init(bar_final, 1);
@@ -306,7 +305,6 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           umma_ss(t_dk, umma_smem_desc(smem_ds + kk * 32, 16, 1024), umma_smem_desc(q_half + kk * 2048, kQPanel, 1024), idesc_dk,
                   it > 0 || kk > 0);
         tc_commit(bar_q_empty + 8 * st);
-        tc_commit(bar_ds_empty);
         (void)phase;
         // dP^T of the next iteration (its TMEM columns hold dQ^T until the drain warps have read it)
         if (more) {
@@ -406,7 +404,8 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         // ---- dS^T = P^T o (dP^T - D), written to shared memory as BF16
         if (!mbar_wait(bar_dp_full, it & 1, wctx, kWaitBwdCompute)) { ok = false; break; }
         // The dS tile of the previous iteration must have been consumed by its dK and dQ MMAs.
-        if (it > 0 && !mbar_wait(bar_ds_empty, (it - 1) & 1, wctx, kWaitBwdCompute)) { ok = false; break; }
+        // (announced by the commit that releases the Q stage of that iteration, issued after the same MMAs)
+        if (it > 0 && !mbar_wait(bar_q_empty + 8 * ((it - 1) & 1), ((it - 1) >> 1) & 1, wctx, kWaitBwdCompute)) { ok = false; break; }
         tc_fence_after();
         float dp[kCols];
         tmem_ld16(t_dp + cb, reinterpret_cast<uint32_t*>(dp));
