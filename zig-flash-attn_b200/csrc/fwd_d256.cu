@@ -11,7 +11,7 @@
 // One 128-row query stage with the score tile double-buffered: the MMA warp issues S(n + 2) right after O += P(n) V_n, so
 // the softmax of block n + 1 overlaps the PV product of block n and the scores of block n + 2.
 // Shared memory: Q 64 KB, one K slot of 64 KB (128 keys x 256 columns; the next K block is loaded as soon as the score
-// MMA of the current one has completed) and a ring of three V slots of 32 KB (64 keys x 256 columns each).
+// MMA of the current one has completed, which the loader learns from the barrier of the score buffer) and a ring of three V slots of 32 KB (64 keys x 256 columns each).
 // Warps 0-3: softmax and epilogue (thread = query row), warp 4: MMA issue, warp 5: TMA loads, warps 6-7: spare.
 #include "fwd_common.cuh"
 
@@ -43,7 +43,7 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t smem_k = smem_q + kQBytes;
   const uint32_t smem_v = smem_k + kKBytes;
   const uint32_t bars = smem_v + NV * kVBytes;
-  const uint32_t bar_q_full = bars, bar_q_empty = bars + 8, bar_k_full = bars + 16, bar_k_empty = bars + 24;
+  const uint32_t bar_q_full = bars, bar_q_empty = bars + 8, bar_k_full = bars + 16;
   const uint32_t bar_v_full = bars + 32, bar_v_empty = bar_v_full + 8 * NV;  // [NV] each
   const uint32_t bar_s_full = bar_v_empty + 8 * NV;                          // [2]
   const uint32_t bar_p_half = bar_s_full + 16;                               // [2]
@@ -63,7 +63,6 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     mbar_init(bar_q_full, 1);
     mbar_init(bar_q_empty, 1);
     mbar_init(bar_k_full, 1);
-    mbar_init(bar_k_empty, 1);
     for (int i = 0; i < NV; ++i) {
       mbar_init(bar_v_full + 8 * i, 1);
       mbar_init(bar_v_empty + 8 * i, 1);
@@ -103,8 +102,17 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     if (lane == 0) {
       uint32_t k_count = 0, v_count = 0, q_count = 0, drawn = 0;
       bool ok = true;
-      auto load_k = [&](int head, int row, int batch_coord) -> bool {
-        if (!mbar_wait(bar_k_empty, (k_count & 1) ^ 1, wctx, kWaitKvEmpty)) return false;
+      // The K slot is free when the score MMAs of the block before have completed, which is what the barrier of their
+      // score buffer announces: the loader follows those barriers (every completion of both, in order) instead of a
+      // barrier of its own, which saves the MMA stream one tcgen05.commit per key block.
+      uint32_t s_issued[2] = {0, 0};  // score products issued into each buffer so far
+      int prev_buffer = -1;
+      uint32_t prev_phase = 0;
+      auto load_k = [&](int head, int row, int batch_coord, int buffer) -> bool {
+        if (prev_buffer >= 0 && !mbar_wait(bar_s_full + 8 * prev_buffer, prev_phase, wctx, kWaitKvEmpty)) return false;
+        prev_buffer = buffer;
+        prev_phase = s_issued[buffer] & 1;
+        ++s_issued[buffer];
         mbar_expect_tx(bar_k_full, kKBytes);
 #pragma unroll
         for (int h = 0; h < 4; ++h) tma_load_4d(smem_k + h * kKPanel, &map_k, bar_k_full, h * 64, head, row, batch_coord);
@@ -140,14 +148,14 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           tma_load_4d(smem_q + h * kQPanel, &map_q, bar_q_full, h * 64, t.head, t.s.q0 + t.m0, t.s.batch_coord);
         for (int i = 0; ok && i < imin(2, n_blocks); ++i) {
           cur_k.next(&kb);
-          ok = load_k(t.kv_head, kb.row, t.s.batch_coord);
+          ok = load_k(t.kv_head, kb.row, t.s.batch_coord, i);
         }
         for (int n = 0; ok && n < n_blocks; ++n) {
           cur_v.next(&kb);
           ok = load_v_half(t.kv_head, kb.row + 64, t.s.batch_coord) && load_v_half(t.kv_head, kb.row, t.s.batch_coord);
           if (ok && n + 2 < n_blocks) {
             cur_k.next(&kb);
-            ok = load_k(t.kv_head, kb.row, t.s.batch_coord);
+            ok = load_k(t.kv_head, kb.row, t.s.batch_coord, n & 1);
           }
         }
       }
@@ -171,7 +179,6 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           umma_ss(tmem_base + buffer * 128, umma_smem_desc(smem_q + (kk >> 2) * kQPanel + (kk & 3) * 32, 16, 1024),
                   umma_smem_desc(smem_k + (kk >> 2) * kKPanel + (kk & 3) * 32, 16, 1024), idesc_s, kk > 0);
         }
-        tc_commit(bar_k_empty);
         tc_commit(bar_s_full + 8 * buffer);
         trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 100 + ((k_count - 1) % 100));  // S issued
         return true;
