@@ -79,8 +79,10 @@ int b200fa_fwd(const b200fa_fwd_args* args, void* stream);
  * code running under a fixed device-memory plan where every byte is assigned up front, or a host-language binding
  * that owns only the input and output buffers and has no allocator to ask for a workspace. Same arguments and results as b200fa_fwd; `workspace` and
  * `workspace_bytes` are ignored. The work list of a packed batch is kept in a 64 KiB array in device memory owned by
- * the library (held by every GPU that loads it until the process exits), so the batch may need at most 8192 work-list
- * entries, i.e. (total_q + 255 * batch) / 256 <= 8192; larger batches are rejected with B200FA_ERR_INVALID and a
+ * the library (held by every GPU that loads it until the process exits). The limit is
+ * b200fa_fwd_workspace_bytes(problem) <= 65536, i.e. at most 8192 work-list entries: one entry covers 256 query rows
+ * of a sequence at head_dim <= 128 ((total_q + 255 * batch) / 256 <= 8192) and 128 rows at head_dim 256 and 512
+ * ((total_q + 127 * batch) / 128 <= 8192); larger batches are rejected with B200FA_ERR_INVALID and a
  * message. Fixed-length problems need no scratch and have no such limit. The call itself allocates and frees nothing.
  * The first call on each device looks up the array's device address (a synchronous CUDA runtime query), so make that
  * first call before any stream capture begins. All calls on a device share the one array: each call rewrites every

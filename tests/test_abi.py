@@ -72,3 +72,40 @@ def test_invalid_arguments_report_errors_without_a_gpu():
     bad_stride = lib.FwdArgs(problem=problem(), q_stride=lib.Stride3(1, 3, 5))
     assert library.b200fa_fwd(ctypes.byref(bad_stride), None) == -1
     assert "multiples of 8" in lib.last_error()
+
+
+def test_backward_rejects_null_and_misaligned_pointers_without_a_launch():
+    """b200fa_bwd reads and writes through raw 16-byte accesses: a null or misaligned tensor pointer must come back as an
+    error code from the host checks (no CUDA context is needed to reach them), never as a fault on the device."""
+    library = lib.library()
+    aligned = 1 << 20  # a pointer value that passes the alignment checks; nothing dereferences it on these paths
+    names = ("q", "k", "v", "out", "dout", "softmax_lse", "dq", "dk", "dv")
+
+    def arguments(**overrides):
+        fields = {name: aligned for name in names}
+        fields.update(overrides)
+        return lib.BwdArgs(problem=problem(), **fields)
+
+    for name in names:
+        assert library.b200fa_bwd(ctypes.byref(arguments(**{name: None})), None) == -1, name
+        assert "null tensor pointer" in lib.last_error()
+    for name in ("q", "k", "v", "out", "dout", "dq", "dk", "dv"):
+        assert library.b200fa_bwd(ctypes.byref(arguments(**{name: aligned + 8})), None) == -1, name
+        assert "16-byte aligned" in lib.last_error()
+    assert library.b200fa_bwd(ctypes.byref(arguments(softmax_lse=aligned + 2)), None) == -1
+    assert "4-byte aligned" in lib.last_error()
+
+
+def test_noalloc_forward_checks_sizes_before_anything_else():
+    library = lib.library()
+    negative = lib.FwdArgs(problem=problem(batch=-1))
+    assert library.b200fa_fwd_noalloc(ctypes.byref(negative), None) == -1
+    assert "negative sizes" in lib.last_error()
+    # 8192 entries are the limit; entries cover 256 query rows up to head_dim 128 and 128 rows above
+    too_long = lib.FwdArgs(problem=problem(batch=1, seqlen_q=256 * 8192 + 1, seqlen_k=16, cu_seqlens_q=8, cu_seqlens_k=8))
+    assert library.b200fa_fwd_noalloc(ctypes.byref(too_long), None) == -1
+    assert "entries of 256 query rows" in lib.last_error()
+    too_long_256 = lib.FwdArgs(problem=problem(batch=1, seqlen_q=128 * 8192 + 1, seqlen_k=16, head_dim=256,
+                                               cu_seqlens_q=8, cu_seqlens_k=8))
+    assert library.b200fa_fwd_noalloc(ctypes.byref(too_long_256), None) == -1
+    assert "entries of 128 query rows at head_dim 256" in lib.last_error()

@@ -50,6 +50,21 @@ def test_work_list_lists_every_block_once_in_the_defined_order(batch, kind, bloc
     assert np.array_equal(table, oracle.work_list_definition(lengths, other, block, bool(descending), entries))
 
 
+def test_work_list_treats_decreasing_prefix_sums_as_empty_sequences():
+    """A cu_seqlens array that is not non-decreasing describes no batch. Its negative lengths must count as empty
+    sequences, so that no entry lands outside the table (in front of it, with a negative index)."""
+    cu = np.array([0, 600, 300, 900, 800, 1300], dtype=np.int32)  # lengths 600, -300, 600, -100, 500
+    guard, entries = 8, 12
+    table = np.full((guard + entries + guard, 2), -7, dtype=np.int32)
+    body = table[guard : guard + entries]
+    status = lib.library().b200fa_work_list_host(cu.ctypes.data, cu.ctypes.data, 5, 256, 0, entries, body.ctypes.data)
+    assert status == 0
+    assert (table[:guard] == -7).all() and (table[guard + entries :] == -7).all()
+    listed = [tuple(row) for row in body.tolist() if row[0] < 5]
+    assert sorted(listed) == [(0, 0), (0, 1), (0, 2), (2, 0), (2, 1), (2, 2), (4, 0), (4, 1)]
+    assert all(tuple(row) == (5, 0) for row in body.tolist()[len(listed) :])
+
+
 @pytest.mark.parametrize("count", [1, 31, 32, 33, 100])
 def test_metadata_matches_its_definition(count):
     rng = np.random.default_rng(count)

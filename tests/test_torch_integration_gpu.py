@@ -74,3 +74,49 @@ def test_compiled_attention_matches_eager():
     q2, k2, v2 = randn(1, 384, 4, 128), randn(1, 384, 2, 128), randn(1, 384, 2, 128)
     assert torch.equal(compiled(q2, k2, v2), attention(q2, k2, v2))
     torch._dynamo.reset()
+
+
+def symbolic(fake_mode, shape, dynamic, dtype=torch.bfloat16):
+    """A fake CUDA tensor whose dimensions listed in `dynamic` are symbolic sizes of fake_mode's shape environment."""
+    from torch.fx.experimental.symbolic_shapes import DimDynamic, StatelessSymbolicContext
+
+    kinds = [DimDynamic.DYNAMIC if index in dynamic else DimDynamic.STATIC for index in range(len(shape))]
+    return fake_mode.from_tensor(torch.empty(shape, device="cuda", dtype=dtype),
+                                 symbolic_context=StatelessSymbolicContext(dynamic_sizes=kinds))
+
+
+def test_fake_outputs_keep_symbolic_sizes_and_add_no_guards():
+    """Shape functions of the ops under symbolic batch and sequence sizes (reference tests/test_torch.py:427-459): the
+    outputs carry the symbols of their inputs, and tracing forward, backward and the packed backward records no guard
+    on them, so a compiled graph is not specialised to the sizes it was traced with."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    from torch.fx.experimental.symbolic_shapes import ShapeEnv
+
+    scale = 64**-0.5
+    environment = ShapeEnv()
+    fake_mode = FakeTensorMode(shape_env=environment)
+    q = symbolic(fake_mode, (3, 136, 8, 64), (0, 1))
+    k, v = (symbolic(fake_mode, (3, 200, 2, 64), (0, 1)) for _ in range(2))
+    before = len(environment.guards)
+    with fake_mode:
+        out, lse = torch.ops.zigfa.flash_attn_forward(q, k, v, None, None, q.shape[1], k.shape[1], scale, -1, 0)
+        dq, dk, dv = torch.ops.zigfa.flash_attn_backward(out, q, k, v, out, lse, None, None, q.shape[1], k.shape[1],
+                                                         scale, -1, 0)
+        dkv = k.new_empty((*k.shape[:-2], 2, *k.shape[-2:]))
+        torch.ops.zigfa.flash_attn_backward_packed(out, q, k, v, out, lse, None, None, q.shape[1], k.shape[1], scale,
+                                                   -1, 0, dq, dkv)
+    for size in (out.shape[0], out.shape[1], lse.shape[0], lse.shape[2], dq.shape[1], dk.shape[0], dk.shape[1], dv.shape[1]):
+        assert isinstance(size, torch.SymInt)
+    assert len(environment.guards) == before
+
+    # packed (varlen) layout: the token count is the symbolic size
+    environment = ShapeEnv()
+    fake_mode = FakeTensorMode(shape_env=environment)
+    q = symbolic(fake_mode, (310, 8, 64), (0,))
+    k, v = (symbolic(fake_mode, (420, 2, 64), (0,)) for _ in range(2))
+    cu = fake_mode.from_tensor(torch.zeros(6, dtype=torch.int32, device="cuda"))
+    before = len(environment.guards)
+    with fake_mode:
+        out, lse = torch.ops.zigfa.flash_attn_forward(q, k, v, cu, cu, 128, 128, scale, -1, 0)
+    assert isinstance(out.shape[0], torch.SymInt) and isinstance(lse.shape[1], torch.SymInt)
+    assert len(environment.guards) == before

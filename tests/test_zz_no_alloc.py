@@ -19,10 +19,10 @@ from zigfa._impl import lib
 pytestmark = pytest.mark.gpu
 
 
-def forward_arguments(q, k, v, cu_q, cu_k, window, workspace):
+def forward_arguments(q, k, v, cu_q, cu_k, window, workspace, **visibility):
     out = torch.full_like(q, float("nan"))
     lse = torch.full((q.shape[1], q.shape[0]), float("nan"), device=q.device)
-    problem = lib.make_problem(q, k, cu_q, cu_k, q.shape[-1] ** -0.5, *window)
+    problem = lib.make_problem(q, k, cu_q, cu_k, q.shape[-1] ** -0.5, *window, **visibility)
     args = lib.FwdArgs(
         problem=problem, q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), softmax_lse=lse.data_ptr(),
         q_stride=lib.strides3(q, True), k_stride=lib.strides3(k, True), v_stride=lib.strides3(v, True),
@@ -33,7 +33,25 @@ def forward_arguments(q, k, v, cu_q, cu_k, window, workspace):
     return args, out, lse
 
 
-def run_both(lengths, heads_q, heads_kv, head_dim, window, seed):
+def prepared_visibility(cu, visible):
+    """The inter-sequence metadata of a boolean (query sequence, key sequence) matrix, made by the library itself."""
+    count = len(visible)
+    words = (count + 31) // 32
+    rows = [[0] * words for _ in range(count)]
+    for i, j in itertools.product(range(count), repeat=2):
+        if visible[i][j]:
+            rows[i][j // 32] |= 1 << (j % 32)
+    bits = torch.tensor(rows, dtype=torch.int64).to(torch.int32).cuda()
+    bits_t = torch.empty_like(bits)
+    cu_visible_k, cu_visible_q = (torch.empty(count + 1, dtype=torch.int32, device="cuda") for _ in range(2))
+    status = lib.library().b200fa_interseq_metadata(
+        cu.data_ptr(), cu.data_ptr(), bits.data_ptr(), count, bits_t.data_ptr(), cu_visible_k.data_ptr(),
+        cu_visible_q.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert status == 0, lib.last_error()
+    return dict(visibility_bits=bits, visibility_bits_t=bits_t, cu_visible_k=cu_visible_k, cu_visible_q=cu_visible_q)
+
+
+def run_both(lengths, heads_q, heads_kv, head_dim, window, seed, visible=None):
     library = lib.library()
     stream = torch.cuda.current_stream().cuda_stream
     torch.manual_seed(seed)
@@ -41,12 +59,13 @@ def run_both(lengths, heads_q, heads_kv, head_dim, window, seed):
     q = torch.randn(total, heads_q, head_dim, device="cuda", dtype=torch.bfloat16)
     k, v = (torch.randn(total, heads_kv, head_dim, device="cuda", dtype=torch.bfloat16) for _ in range(2))
     cu = torch.tensor([0, *itertools.accumulate(lengths)], dtype=torch.int32, device="cuda")
-    problem = lib.make_problem(q, k, cu, cu, head_dim**-0.5, *window)
+    visibility = {} if visible is None else prepared_visibility(cu, visible)
+    problem = lib.make_problem(q, k, cu, cu, head_dim**-0.5, *window, **visibility)
     workspace = torch.empty(max(library.b200fa_fwd_workspace_bytes(ctypes.byref(problem)), 1), dtype=torch.uint8, device="cuda")
-    regular, out_regular, lse_regular = forward_arguments(q, k, v, cu, cu, window, workspace)
+    regular, out_regular, lse_regular = forward_arguments(q, k, v, cu, cu, window, workspace, **visibility)
     assert library.b200fa_fwd(ctypes.byref(regular), stream) == 0, lib.last_error()
     # no workspace at all: the pointer is null and the size zero
-    bare, out_bare, lse_bare = forward_arguments(q, k, v, cu, cu, window, None)
+    bare, out_bare, lse_bare = forward_arguments(q, k, v, cu, cu, window, None, **visibility)
     assert library.b200fa_fwd_noalloc(ctypes.byref(bare), stream) == 0, lib.last_error()
     torch.cuda.synchronize()
     assert not torch.isnan(out_regular).any()
@@ -58,6 +77,21 @@ def run_both(lengths, heads_q, heads_kv, head_dim, window, seed):
 def test_noalloc_forward_matches_the_regular_entry_point_twice_in_a_row():
     run_both([700, 33, 0, 1500, 256, 911], 8, 2, 128, (-1, 0), seed=11)
     run_both([120, 300], 4, 4, 64, (50, 10), seed=12)
+
+
+def test_noalloc_forward_with_the_smaller_work_items_of_head_dim_256():
+    # head_dim 256 draws work items of 128 query rows (twice the entries per token), packed batch, then a shorter one
+    run_both([300, 0, 129, 1024, 77], 4, 2, 256, (-1, 0), seed=13)
+    run_both([128, 65], 2, 1, 256, (-1, -1), seed=14)
+
+
+def test_noalloc_forward_with_an_inter_sequence_batch():
+    # shared prefixes: the work list is sorted by visible key tokens (cu_visible_k), not by the sequences' own lengths
+    lengths = [512, 100, 37, 300, 64, 200]
+    prefix_of = [0, 0, 0, 3, 3, 3]
+    visible = [[j == i or j == prefix_of[i] for j in range(len(lengths))] for i in range(len(lengths))]
+    run_both(lengths, 8, 2, 128, (-1, 0), seed=15, visible=visible)
+    run_both(lengths[:3], 4, 4, 256, (-1, 0), seed=16, visible=[row[:3] for row in visible[:3]])
 
 
 def test_noalloc_forward_refuses_batches_beyond_its_scratch():

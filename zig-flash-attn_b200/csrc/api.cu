@@ -1,4 +1,5 @@
 // C-ABI entry points (include/b200fa.h): argument validation, workspace sizing and dispatch to the launchers.
+#include <atomic>
 #include <mutex>
 
 #include "common.h"
@@ -70,17 +71,26 @@ int encode_tensor_map(CUtensorMap* map, const void* base, CUtensorMapDataType ty
   return B200FA_OK;
 }
 
+// The per-device caches of the library (SM counts, symbol addresses, "attribute already set" records) are read and
+// filled under this one mutex: the entry points may be called from several host threads at once. It is held for a
+// few loads on the launch path and for one CUDA query the first time a device is seen.
+std::mutex& cache_mutex() {
+  static std::mutex mutex;
+  return mutex;
+}
+
 int device_sm_count(int* count) {
   static int cached[64] = {0};
   int device = 0;
   B200FA_CUDA_CHECK(cudaGetDevice(&device));
-  if (device < 64 && cached[device] > 0) {
+  std::lock_guard<std::mutex> lock(cache_mutex());
+  if (device >= 0 && device < 64 && cached[device] > 0) {
     *count = cached[device];
     return B200FA_OK;
   }
   int value = 0;
   B200FA_CUDA_CHECK(cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device));
-  if (device < 64) cached[device] = value;
+  if (device >= 0 && device < 64) cached[device] = value;
   *count = value;
   return B200FA_OK;
 }
@@ -88,6 +98,7 @@ int device_sm_count(int* count) {
 int set_dynamic_smem_once(const void* kernel, int bytes, bool (&done)[64]) {
   int device = 0;
   B200FA_CUDA_CHECK(cudaGetDevice(&device));
+  std::lock_guard<std::mutex> lock(cache_mutex());
   if (device >= 0 && device < 64 && done[device]) return B200FA_OK;
   B200FA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
   if (device >= 0 && device < 64) done[device] = true;
@@ -101,19 +112,20 @@ int* device_status_word() {
     set_error("cudaGetDevice failed");
     return nullptr;
   }
-  if (device < 64 && cached[device]) return cached[device];
+  std::lock_guard<std::mutex> lock(cache_mutex());
+  if (device >= 0 && device < 64 && cached[device]) return cached[device];
   void* address = nullptr;
   cudaError_t status = cudaGetSymbolAddress(&address, g_device_status);
   if (status != cudaSuccess) {
     set_error("cudaGetSymbolAddress failed: %s", cudaGetErrorString(status));
     return nullptr;
   }
-  if (device < 64) cached[device] = static_cast<int*>(address);
+  if (device >= 0 && device < 64) cached[device] = static_cast<int*>(address);
   return static_cast<int*>(address);
 }
 
-static long long* g_trace = nullptr;
-long long* trace_buffer() { return g_trace; }
+static std::atomic<long long*> g_trace{nullptr};
+long long* trace_buffer() { return g_trace.load(std::memory_order_relaxed); }
 
 int launch_fwd(const b200fa_fwd_args& args, cudaStream_t stream);
 int launch_bwd(const b200fa_bwd_args& args, cudaStream_t stream);
@@ -184,7 +196,7 @@ int b200fa_fwd(const b200fa_fwd_args* args, void* stream) {
 }
 
 int b200fa_set_trace(void* counters) {
-  g_trace = static_cast<long long*>(counters);
+  g_trace.store(static_cast<long long*>(counters), std::memory_order_relaxed);
   return B200FA_OK;
 }
 
@@ -208,6 +220,17 @@ int b200fa_bwd(const b200fa_bwd_args* args, void* stream) {
                      strides_ok(args->dk_stride) && strides_ok(args->dv_stride),
                  "tensor strides must be multiples of 8 elements");
   if (p.batch == 0) return B200FA_OK;
+  // The kernels read and write these tensors with 16-byte accesses and no further checks: refuse here what would
+  // otherwise fault on the device. (q, k, v, dout go through tensor maps, whose encoder checks them once more.)
+  const bool have_q = p.seqlen_q > 0, have_k = p.seqlen_k > 0;
+  B200FA_REQUIRE(!have_q || (args->q && args->out && args->dout && args->softmax_lse && args->dq),
+                 "null tensor pointer (q, out, dout, softmax_lse and dq are required when there are query rows)");
+  B200FA_REQUIRE(!have_k || (args->k && args->v && args->dk && args->dv),
+                 "null tensor pointer (k, v, dk and dv are required when there are key rows)");
+  const void* aligned16[] = {args->q, args->k, args->v, args->out, args->dout, args->dq, args->dk, args->dv};
+  for (const void* pointer : aligned16)
+    B200FA_REQUIRE(reinterpret_cast<uintptr_t>(pointer) % 16 == 0, "tensor pointers must be 16-byte aligned");
+  B200FA_REQUIRE(reinterpret_cast<uintptr_t>(args->softmax_lse) % 4 == 0, "softmax_lse must be 4-byte aligned");
   return launch_bwd(*args, static_cast<cudaStream_t>(stream));
 }
 

@@ -8,6 +8,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <mutex>
+
 #include "../../include/b200fa.h"
 #include "attn_index.h"
 
@@ -39,6 +41,9 @@ int encode_tensor_map(CUtensorMap* map, const void* base, CUtensorMapDataType ty
                       int64_t batch_stride, int box_cols, int box_rows);
 
 Problem to_problem(const b200fa_problem& in);
+
+// Guards every per-device cache of the library (see api.cu).
+std::mutex& cache_mutex();
 
 int device_sm_count(int* count);
 // Raises the dynamic shared-memory limit of `kernel` once per device (function attributes are per device; `done` is

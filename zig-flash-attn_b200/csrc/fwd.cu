@@ -481,24 +481,33 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 
 // -------------------------------------------------------------------------------------------------- host side
 
-// Work-item counters of the persistent kernels: a ring inside the library (the library allocates no device memory).
-// Every launch takes the next slot and zeroes it with a memset node on its own stream ahead of the kernel, so two
-// launches share a slot only if kTileCounters other launches were issued in between.
+// Work-item counters of the persistent kernels: a ring of counters per device inside the library (the library
+// allocates no device memory). Every launch takes the next slot of its device's ring and zeroes it with a memset node
+// on its own stream ahead of the kernel. Two launches use the same slot when kTileCounters other forward launches were
+// issued on that device in between, or when one of them is a replay of a captured graph (a graph keeps the slot it was
+// captured with). Sharing is harmless while the two are ordered on the GPU; two kernels that share a slot and overlap
+// in time (different streams, no ordering) would draw from one counter and skip or repeat work items. The contract
+// is therefore: per device, at most kTileCounters forward launches may be in flight or held in captured graphs that
+// can run concurrently with later launches.
 constexpr unsigned kTileCounters = 4096;
 static __device__ int g_tile_counters[kTileCounters];
 
 int acquire_tile_counter(cudaStream_t stream, int** counter) {
   static int* base[64] = {nullptr};
-  static std::atomic<unsigned> next{0};
+  static unsigned next[64] = {0};
   int device = 0;
   B200FA_CUDA_CHECK(cudaGetDevice(&device));
   B200FA_REQUIRE(device >= 0 && device < 64, "device ordinal %d is out of range", device);
-  if (!base[device]) {
-    void* address = nullptr;
-    B200FA_CUDA_CHECK(cudaGetSymbolAddress(&address, g_tile_counters));
-    base[device] = static_cast<int*>(address);
+  int* slot = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(cache_mutex());
+    if (!base[device]) {
+      void* address = nullptr;
+      B200FA_CUDA_CHECK(cudaGetSymbolAddress(&address, g_tile_counters));
+      base[device] = static_cast<int*>(address);
+    }
+    slot = base[device] + next[device]++ % kTileCounters;
   }
-  int* slot = base[device] + next.fetch_add(1) % kTileCounters;
   B200FA_CUDA_CHECK(cudaMemsetAsync(slot, 0, sizeof(int), stream));
   *counter = slot;
   return B200FA_OK;
@@ -625,7 +634,7 @@ int launch_fwd(const b200fa_fwd_args& a, cudaStream_t stream) {
 // the work list of a packed (varlen / inter-sequence) batch; here it lives in a fixed array in device memory that
 // belongs to the library. Every GPU that loads the library holds these 64 KiB until the process exits.
 namespace b200fa {
-constexpr int kStaticWorkListEntries = 8192;  // (sequence, block) pairs; one entry covers 256 query rows
+constexpr int kStaticWorkListEntries = 8192;  // (sequence, block) pairs; one entry covers 256 query rows (128 at head_dim 256 and 512)
 static __device__ __align__(256) int32_t g_static_work_list[2 * kStaticWorkListEntries];
 
 // Device address of the array on the current device. `g_static_work_list` as written in host code is only a host-side
@@ -635,6 +644,7 @@ static int static_work_list(int32_t** address) {
   int device = 0;
   B200FA_CUDA_CHECK(cudaGetDevice(&device));
   B200FA_REQUIRE(device >= 0 && device < 64, "device index %d is out of range", device);
+  std::lock_guard<std::mutex> lock(cache_mutex());
   if (!cached[device]) {
     int32_t* pointer = nullptr;
     B200FA_CUDA_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&pointer), g_static_work_list));
@@ -649,11 +659,15 @@ extern "C" int b200fa_fwd_noalloc(const b200fa_fwd_args* args, void* stream) {
   using namespace b200fa;
   B200FA_REQUIRE(args != nullptr, "null arguments");
   const b200fa_problem& problem = args->problem;
+  B200FA_REQUIRE(problem.batch >= 0 && problem.seqlen_q >= 0 && problem.seqlen_k >= 0, "negative sizes");
   const size_t needed = b200fa_fwd_workspace_bytes(&problem);
+  const int tile_rows = problem.head_dim >= 256 ? kBlockM : kFwdTileM;
   B200FA_REQUIRE(needed <= sizeof(int32_t) * 2 * kStaticWorkListEntries,
-                 "b200fa_fwd_noalloc: the batch needs a work list of %zu bytes (%zu entries of 256 query rows) but the "
-                 "built-in scratch holds %zu bytes (%d entries); use b200fa_fwd with a caller-provided workspace",
-                 needed, needed / 8, sizeof(int32_t) * 2 * kStaticWorkListEntries, kStaticWorkListEntries);
+                 "b200fa_fwd_noalloc: the batch needs a work list of %zu bytes (%zu entries of %d query rows at "
+                 "head_dim %d) but the built-in scratch holds %zu bytes (%d entries); use b200fa_fwd with a "
+                 "caller-provided workspace",
+                 needed, needed / 8, tile_rows, problem.head_dim, sizeof(int32_t) * 2 * kStaticWorkListEntries,
+                 kStaticWorkListEntries);
   int32_t* scratch = nullptr;
   const int status = static_work_list(&scratch);
   if (status != B200FA_OK) return status;

@@ -118,8 +118,9 @@ __device__ __forceinline__ FwdTile decode_tile(const FwdParams& p, int tile, int
 int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim, int tile_rows, int kv_box_rows,
                     FwdParams* p, CUtensorMap* map_q, CUtensorMap* map_k, CUtensorMap* map_v, bool* nothing_to_do,
                     int v_box_rows = 0 /* rows per TMA box of V when they differ from those of K */);
-// A zeroed work-item counter for one launch on `stream` (a slot of a ring of counters inside the library, reset by a
-// memset node ahead of the kernel, so launches on different streams never share one). Defined in fwd.cu.
+// A zeroed work-item counter for one launch on `stream`: the next slot of the device's ring of 4096 counters inside the
+// library, reset by a memset node ahead of the kernel. Launches share a slot only 4096 launches apart (or through a
+// captured graph, which keeps its slot); see the contract at its definition in fwd.cu.
 int acquire_tile_counter(cudaStream_t stream, int** counter);
 int launch_fwd_256(const b200fa_fwd_args& a, cudaStream_t stream);
 int launch_fwd_256_pair(const b200fa_fwd_args& a, cudaStream_t stream);  // two-CTA variant (fwd_d256_pair.cu)

@@ -36,7 +36,12 @@ enum WaitCode : int {
   kWaitTile = 13,
 };
 
-constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // 2 s per wait
+// Time a single wait may take before it gives up: 2 s, far above anything a healthy launch needs. A test build can
+// shorten it (-DB200FA_WAIT_BUDGET_NS=...) to watch a wait run out.
+#ifndef B200FA_WAIT_BUDGET_NS
+#define B200FA_WAIT_BUDGET_NS 2000000000ull
+#endif
+constexpr unsigned long long kWaitBudgetNs = B200FA_WAIT_BUDGET_NS;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

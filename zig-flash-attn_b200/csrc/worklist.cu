@@ -35,7 +35,9 @@ work_list_kernel(const int32_t* __restrict__ cu, const int32_t* __restrict__ cu_
     if (valid) {
       const uint32_t other = static_cast<uint32_t>(cu_other[i + 1] - cu_other[i]);
       key = kClasses - 1 - length_class(other);
-      blocks = ceil_div(cu[i + 1] - cu[i], block_rows);
+      // A prefix-sum array that is not non-decreasing describes no batch; its negative lengths count as empty
+      // sequences, so that no entry index can become negative (the kernels that read the list then skip them).
+      blocks = ceil_div(imax(cu[i + 1] - cu[i], 0), block_rows);
     }
     keys[tid] = key;
     __syncthreads();
@@ -64,7 +66,7 @@ work_list_kernel(const int32_t* __restrict__ cu, const int32_t* __restrict__ cu_
     const int sequence = order[tid];
     for (int b = 0; b < my_blocks; ++b) {
       const int entry = start + b;
-      if (entry < num_entries) table[entry] = make_int2(sequence, descending ? my_blocks - 1 - b : b);
+      if (entry >= 0 && entry < num_entries) table[entry] = make_int2(sequence, descending ? my_blocks - 1 - b : b);
     }
     __syncthreads();
     if (tid == kListThreads - 1) written_shared = base + value;
@@ -204,7 +206,7 @@ int b200fa_work_list_host(const int32_t* cu_seqlens, const int32_t* cu_seqlens_o
              length_class(static_cast<uint32_t>(cu_seqlens_other[y + 1] - cu_seqlens_other[y]));
     });
     for (int sequence : order) {
-      const int blocks = ceil_div(cu_seqlens[sequence + 1] - cu_seqlens[sequence], block_rows);
+      const int blocks = ceil_div(imax(cu_seqlens[sequence + 1] - cu_seqlens[sequence], 0), block_rows);  // as the kernel
       for (int b = 0; b < blocks; ++b, ++written) {
         if (written < num_entries) {
           table[2 * written] = sequence;
