@@ -185,6 +185,16 @@ struct KeyCursor {
 
   B200FA_HD bool bit(int j) const { return (static_cast<uint32_t>(p->bits[seq * p->words + (j >> 5)]) >> (j & 31)) & 1u; }
 
+  // Split-KV: keeps share `split` of `splits` equal shares of the key blocks (call right after init; problems with
+  // one key run only, i.e. without visibility bits). Shares of a run shorter than `splits` blocks may be empty.
+  B200FA_HD void restrict_to_share(int split, int splits) {
+    // 32-bit arithmetic on purpose (a run has far fewer than 2^26 blocks and there are at most 32 shares): a 64-bit
+    // division is a subroutine call, which the warp-specialised kernels avoid.
+    const unsigned n = static_cast<unsigned>(blk_end - blk), first = static_cast<unsigned>(blk);
+    blk = static_cast<int>(first + n * static_cast<unsigned>(split) / static_cast<unsigned>(splits));
+    blk_end = static_cast<int>(first + n * static_cast<unsigned>(split + 1) / static_cast<unsigned>(splits));
+  }
+
   // Finds the next non-empty run at or after `scan`. Returns false when there is none.
   B200FA_HD bool next_run() {
     const int n = p->batch;

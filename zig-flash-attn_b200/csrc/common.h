@@ -46,6 +46,9 @@ Problem to_problem(const b200fa_problem& in);
 std::mutex& cache_mutex();
 
 int device_sm_count(int* count);
+// Bytes of partial results the split-KV forward path wants for this problem (0 = the problem is not split). Defined in
+// fwd.cu; a pure function of the shapes.
+size_t fwd_split_workspace_bytes(const b200fa_problem& problem);
 // Raises the dynamic shared-memory limit of `kernel` once per device (function attributes are per device; `done` is
 // the caller's per-kernel record, indexed by device ordinal).
 int set_dynamic_smem_once(const void* kernel, int bytes, bool (&done)[64]);

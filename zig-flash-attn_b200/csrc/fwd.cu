@@ -140,10 +140,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       };
       uint32_t drawn = 0;
       for (int tile; ok && (tile = tiles.push(drawn, p.tile_counter, p.num_tiles, wctx)) >= 0;) {
-        FwdTile t = decode_tile(p, tile);
+        FwdTile t = decode_tile(p, tile / p.splits);
         if (!t.valid) continue;
         KeyCursor cur;
         cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kFwdTileM, t.s.lq));
+        if (p.splits > 1) cur.restrict_to_share(tile % p.splits, p.splits);
         OtherBlock kb;
         if (!cur.next(&kb)) continue;
         if (!mbar_wait(bar_q_empty, (q_count & 1) ^ 1, wctx, kWaitQEmpty)) { ok = false; break; }
@@ -208,10 +209,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       };
       uint32_t popped = 0;
       for (int tile; ok && (tile = tiles.pop_thread(popped, wctx)) >= 0;) {
-        FwdTile t = decode_tile(p, tile);
+        FwdTile t = decode_tile(p, tile / p.splits);
         if (!t.valid) continue;
         KeyCursor cur;
         cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kFwdTileM, t.s.lq));
+        if (p.splits > 1) cur.restrict_to_share(tile % p.splits, p.splits);
         OtherBlock kb;
         if (!cur.next(&kb)) continue;
         const uint32_t q_phase = q_count & 1;
@@ -286,11 +288,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     bool ok = true;
     uint32_t popped = 0;
     for (int tile; ok && (tile = tiles.pop_warp(popped, wctx)) >= 0;) {
-      FwdTile t = decode_tile(p, tile);
+      FwdTile t = decode_tile(p, tile / p.splits);
       if (!t.valid) continue;
       const int row = t.m0 + stage * kBlockM + row_in_stage;  // row within the sequence
       KeyCursor cur;
       cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kFwdTileM, t.s.lq));
+      const int split = p.splits > 1 ? tile % p.splits : 0;
+      if (p.splits > 1) cur.restrict_to_share(split, p.splits);
       const int band_lo = cur.band.lo(row), band_hi = cur.band.hi(row);
       float m = -INFINITY, l = 0.f;
       int tile_blocks = 0;
@@ -426,12 +430,25 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       __nv_bfloat16* o_row = p.o + t.s.batch_coord * p.o_batch_stride + (int64_t)(t.s.q0 + row) * p.o_row_stride +
                              (int64_t)t.head * p.o_head_stride;
       float* lse_ptr = p.lse + t.s.batch_coord * p.lse_batch_stride + (int64_t)t.head * p.lse_head_stride + t.s.q0 + row;
+      // Split-KV: this share's normalised output (fp32) and log-sum-exp go to the partial buffers instead.
+      float* o_part = nullptr;
+      if (p.splits > 1) {
+        const int64_t global_row = (int64_t)t.s.batch_coord * pr.seqlen_q + row;
+        o_part = p.o_partial + (((int64_t)split * p.partial_rows + global_row) * pr.heads_q + t.head) * p.head_dim;
+        lse_ptr = p.lse_partial + ((int64_t)split * pr.heads_q + t.head) * p.partial_rows + global_row;
+      }
       if (tile_blocks == 0) {
         if (row_valid) {
           const uint4 zero = make_uint4(0, 0, 0, 0);
+          if (o_part) {
 #pragma unroll
-          for (int c = 0; c < D / 8; ++c)
-            if (8 * c < p.head_dim) reinterpret_cast<uint4*>(o_row)[c] = zero;
+            for (int c = 0; c < D / 4; ++c)
+              if (4 * c < p.head_dim) reinterpret_cast<uint4*>(o_part)[c] = zero;
+          } else {
+#pragma unroll
+            for (int c = 0; c < D / 8; ++c)
+              if (8 * c < p.head_dim) reinterpret_cast<uint4*>(o_row)[c] = zero;
+          }
           *lse_ptr = -INFINITY;
         }
         continue;
@@ -446,7 +463,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         uint32_t o[32];
         tmem_ld32(t_o + 32 * c, o);
         tc_wait_ld();
-        if (row_valid) {
+        if (row_valid && o_part) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 v = make_float4(__uint_as_float(o[4 * i + 0]) * inv, __uint_as_float(o[4 * i + 1]) * inv,
+                                         __uint_as_float(o[4 * i + 2]) * inv, __uint_as_float(o[4 * i + 3]) * inv);
+            if (32 * c + 4 * i < p.head_dim) reinterpret_cast<float4*>(o_part)[8 * c + i] = v;
+          }
+        } else if (row_valid) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             uint4 v;
@@ -513,6 +537,81 @@ int acquire_tile_counter(cudaStream_t stream, int** counter) {
   return B200FA_OK;
 }
 
+// ---- split-KV (short queries over long keys; reference src/zigfa/_impl/forward.py:51-69)
+// With few query tiles and many key blocks most SMs would idle while a few walk long key ranges: the key blocks of a
+// tile are then dealt out in `splits` equal shares to as many work items, and split_combine_kernel merges the shares.
+// The plan is a pure function of the shapes (it assumes the 148 SMs of a B200), so the workspace size it implies can be
+// computed without a device.
+constexpr int kPlanSms = 148;
+struct SplitPlan {
+  int splits;
+  size_t o_bytes, lse_bytes;
+};
+static SplitPlan plan_split(const b200fa_problem& bp) {
+  SplitPlan plan{1, 0, 0};
+  if (bp.cu_seqlens_q || bp.visibility_bits || bp.head_dim > 128 || bp.batch <= 0 || bp.seqlen_q <= 0) return plan;
+  const int64_t tiles = (int64_t)bp.batch * bp.heads_q * ceil_div(bp.seqlen_q, kFwdTileM);
+  int64_t keys = bp.seqlen_k;
+  if (bp.window_left >= 0) {
+    const int64_t reach = (int64_t)bp.window_left + imin(bp.seqlen_q, kFwdTileM) + imax(bp.window_right, 0);
+    keys = keys < reach ? keys : reach;
+  }
+  const int64_t blocks = (keys + kBlockN - 1) / kBlockN;
+  // The reference's rule (src/zigfa/_impl/forward.py:23-25,60-62): keys >= 4 x queries, at least 256 keys per share.
+  if (2 * tiles > kPlanSms || blocks < 4 || keys < 4 * (int64_t)bp.seqlen_q) return plan;
+  int64_t splits = kPlanSms / tiles;
+  if (splits > blocks / 2) splits = blocks / 2;  // at least two key blocks per share
+  if (splits > 32) splits = 32;
+  if (splits < 2) return plan;
+  plan.splits = (int)splits;
+  const size_t rows = (size_t)bp.batch * bp.seqlen_q;
+  plan.o_bytes = ((size_t)splits * rows * bp.heads_q * bp.head_dim * 4 + 255) & ~size_t(255);
+  plan.lse_bytes = ((size_t)splits * rows * bp.heads_q * 4 + 255) & ~size_t(255);
+  return plan;
+}
+size_t fwd_split_workspace_bytes(const b200fa_problem& bp) {
+  const SplitPlan plan = plan_split(bp);
+  return plan.o_bytes + plan.lse_bytes;
+}
+
+// out = sum_i w_i O_i / sum_i w_i with w_i = exp(lse_i - max lse), lse = max + log(sum w_i); a row no share saw keeps
+// zeros and -inf. One thread per (row, head, group of 4 columns).
+__global__ void __launch_bounds__(256) split_combine_kernel(const float* __restrict__ o_partial,
+                                                            const float* __restrict__ lse_partial, int splits,
+                                                            int64_t rows, int seqlen_q, int heads, int head_dim,
+                                                            __nv_bfloat16* __restrict__ out, int64_t o_bs, int64_t o_rs,
+                                                            int64_t o_hs, float* __restrict__ lse, int64_t lse_bs,
+                                                            int64_t lse_hs) {
+  const int groups = head_dim / 4;
+  const int64_t index = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (index >= rows * heads * groups) return;
+  const int g = (int)(index % groups);
+  const int head = (int)((index / groups) % heads);
+  const int64_t row = index / groups / heads;
+  float top = -INFINITY;
+  for (int i = 0; i < splits; ++i) top = fmaxf(top, lse_partial[((int64_t)i * heads + head) * rows + row]);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float total = 0.f;
+  if (top != -INFINITY) {
+    for (int i = 0; i < splits; ++i) {
+      const float w = __expf(lse_partial[((int64_t)i * heads + head) * rows + row] - top);
+      const float4 o = *reinterpret_cast<const float4*>(o_partial + (((int64_t)i * rows + row) * heads + head) * head_dim + 4 * g);
+      acc.x += w * o.x;
+      acc.y += w * o.y;
+      acc.z += w * o.z;
+      acc.w += w * o.w;
+      total += w;
+    }
+  }
+  const float inv = total > 0.f ? 1.f / total : 0.f;
+  const int64_t b = row / seqlen_q, r = row - b * seqlen_q;
+  uint2 packed;
+  packed.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+  packed.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+  *reinterpret_cast<uint2*>(out + b * o_bs + r * o_rs + (int64_t)head * o_hs + 4 * g) = packed;
+  if (g == 0) lse[b * lse_bs + (int64_t)head * lse_hs + r] = total > 0.f ? top + logf(total) : -INFINITY;
+}
+
 int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim, int tile_rows, int kv_box_rows,
                     FwdParams* params, CUtensorMap* map_q, CUtensorMap* map_k, CUtensorMap* map_v, bool* nothing_to_do,
                     int v_box_rows) {
@@ -532,6 +631,10 @@ int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim,
   p.lse_batch_stride = packed ? 0 : a.lse_stride[0];
   p.lse_head_stride = a.lse_stride[1];
   p.work_list = nullptr;
+  p.splits = 1;
+  p.o_partial = nullptr;
+  p.lse_partial = nullptr;
+  p.partial_rows = 0;
   p.tile_counter = nullptr;
   p.m_blocks = 0;
   p.head_dim = bp.head_dim;
@@ -596,9 +699,30 @@ static int launch_fwd_d(const b200fa_fwd_args& a, cudaStream_t stream) {
   int sms = 0;
   status = device_sm_count(&sms);
   if (status != B200FA_OK) return status;
+  // Split-KV when the plan asks for it and the caller's workspace has room for the partial results (an entry point
+  // that brings its own small scratch runs the same problem unsplit).
+  const b200fa_problem& bp = a.problem;
+  const SplitPlan plan = plan_split(bp);
+  const bool split = plan.splits > 1 && a.workspace && a.workspace_bytes >= plan.o_bytes + plan.lse_bytes &&
+                     reinterpret_cast<uintptr_t>(a.workspace) % 16 == 0;
+  if (split) {
+    p.splits = plan.splits;
+    p.o_partial = static_cast<float*>(a.workspace);
+    p.lse_partial = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + plan.o_bytes);
+    p.partial_rows = (int64_t)bp.batch * bp.seqlen_q;
+    p.num_tiles *= plan.splits;
+  }
   const int grid = p.num_tiles < sms ? p.num_tiles : sms;
   fwd_kernel<D><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
   B200FA_CUDA_CHECK(cudaGetLastError());
+  if (split) {
+    const int64_t threads = p.partial_rows * bp.heads_q * (bp.head_dim / 4);
+    split_combine_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(
+        p.o_partial, p.lse_partial, plan.splits, p.partial_rows, bp.seqlen_q, bp.heads_q, bp.head_dim,
+        static_cast<__nv_bfloat16*>(a.out), a.out_stride[0], a.out_stride[1], a.out_stride[2], a.softmax_lse,
+        a.lse_stride[0], a.lse_stride[1]);
+    B200FA_CUDA_CHECK(cudaGetLastError());
+  }
   return B200FA_OK;
 }
 
@@ -660,7 +784,9 @@ extern "C" int b200fa_fwd_noalloc(const b200fa_fwd_args* args, void* stream) {
   B200FA_REQUIRE(args != nullptr, "null arguments");
   const b200fa_problem& problem = args->problem;
   B200FA_REQUIRE(problem.batch >= 0 && problem.seqlen_q >= 0 && problem.seqlen_k >= 0, "negative sizes");
-  const size_t needed = b200fa_fwd_workspace_bytes(&problem);
+  // Only the work list of a packed batch is scratch this entry point must provide; the partial results the split-KV path
+  // of a fixed-length problem would like are optional (without room for them the problem runs unsplit).
+  const size_t needed = problem.cu_seqlens_q ? b200fa_fwd_workspace_bytes(&problem) : 0;
   const int tile_rows = problem.head_dim >= 256 ? kBlockM : kFwdTileM;
   B200FA_REQUIRE(needed <= sizeof(int32_t) * 2 * kStaticWorkListEntries,
                  "b200fa_fwd_noalloc: the batch needs a work list of %zu bytes (%zu entries of %d query rows at "

@@ -19,6 +19,12 @@ struct FwdParams {
   int head_dim;           // columns of the tensors (<= the compiled width; TMA zero-fills the columns in between)
   int* status;            // device status word of the library
   long long* trace;       // optional cycle counters of tuning builds (slots 16-23), null = off
+  // Split-KV (fwd.cu, short queries over long keys): a work item is (tile, share of the key blocks); every share writes
+  // its normalised partial output and its log-sum-exp here and a second kernel merges them. splits == 1: off.
+  int splits;
+  float* o_partial;       // (splits, rows, heads_q, head_dim) fp32, rows = batch * seqlen_q
+  float* lse_partial;     // (splits, heads_q, rows) fp32
+  int64_t partial_rows;
 };
 
 struct FwdTile {
