@@ -415,3 +415,38 @@ def test_head_dim_256_two_cta_variant_matches_the_single_cta_kernel(tmp_path):
     for name, (out, lse) in outputs["0"].items():
         out_pair, lse_pair = outputs["1"][name]
         assert torch.equal(out, out_pair) and torch.equal(lse, lse_pair), name
+
+
+def test_concurrent_host_threads_on_their_own_streams():
+    """The entry points may be called from several host threads at once (per-device caches behind a mutex, a work-item
+    counter per launch): four threads, each on its own stream, run forward passes of different shapes in a loop and
+    every result equals the one computed alone."""
+    import threading
+
+    shapes = [(2, 384, 4, 2, 128), (1, 1000, 8, 8, 64), (3, 256, 6, 2, 128), (1, 2048, 4, 1, 128)]
+    inputs, expected = [], []
+    for index, (batch, seqlen, heads_q, heads_kv, d) in enumerate(shapes):
+        torch.manual_seed(100 + index)
+        q = randn(batch, seqlen, heads_q, d)
+        k, v = randn(batch, seqlen, heads_kv, d), randn(batch, seqlen, heads_kv, d)
+        inputs.append((q, k, v))
+        expected.append(zigfa.flash_attn_func(q, k, v, causal=True))
+    torch.cuda.synchronize()
+    failures = []
+
+    def worker(index):
+        stream = torch.cuda.Stream()
+        q, k, v = inputs[index]
+        with torch.cuda.stream(stream):
+            for _ in range(25):
+                out = zigfa.flash_attn_func(q, k, v, causal=True)
+            stream.synchronize()
+        if not torch.equal(out, expected[index]):
+            failures.append(index)
+
+    threads = [threading.Thread(target=worker, args=(index,)) for index in range(len(shapes))]
+    for thread in threads:
+        thread.start()
+    for thread in threads:
+        thread.join()
+    assert not failures, f"results of threads {failures} differ from the single-threaded ones"
