@@ -61,6 +61,23 @@ def test_fixed_length_matches_oracle(head_dim, kind):
                            notes=f"[{kind} {seqlen_q}x{seqlen_k} {heads_name} d{head_dim}]")
 
 
+def test_packed_query_heads_equal_the_unpacked_instance_bit_for_bit():
+    """With a power-of-two number of query heads per key head the forward kernel packs the heads of a group into the
+    rows of a work item (the reference tests the same equality for its packed-GQA instances, tests/test_backward.py:138-159).
+    A row's arithmetic does not depend on which rows share its tile, so the result equals, bit for bit, that of the
+    same problem given as multi-head attention with every key head repeated (which is not packed)."""
+    cases = [(2, 300, 555, 8, 2, 128, (-1, 0)), (1, 1024, 1024, 16, 1, 64, (100, 0)), (1, 300, 600, 128, 1, 128, (-1, -1)),
+             (2, 513, 513, 4, 2, 96, (-1, 0)), (1, 2048, 2048, 8, 2, 128, (-1, 17))]
+    for batch, seqlen_q, seqlen_k, heads_q, heads_kv, d, window in cases:
+        torch.manual_seed(seqlen_q + heads_q)
+        q, k, v = randn(batch, seqlen_q, heads_q, d), randn(batch, seqlen_k, heads_kv, d), randn(batch, seqlen_k, heads_kv, d)
+        group = heads_q // heads_kv
+        out, lse = zigfa.flash_attn_func(q, k, v, window_size=window, return_attn_probs=True)
+        wide_k, wide_v = k.repeat_interleave(group, dim=2), v.repeat_interleave(group, dim=2)
+        out_wide, lse_wide = zigfa.flash_attn_func(q, wide_k, wide_v, window_size=window, return_attn_probs=True)
+        assert torch.equal(out, out_wide) and torch.equal(lse, lse_wide), (heads_q, heads_kv, d, window)
+
+
 def test_large_gqa_groups_and_long_sequences():
     for batch, heads_q, heads_kv, seqlen in [(3, 18, 6, 4096), (8, 16, 2, 2048), (1, 8, 2, 4096), (1, 32, 1, 1024)]:
         torch.manual_seed(seqlen + heads_q)

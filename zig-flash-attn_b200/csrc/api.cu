@@ -37,7 +37,7 @@ static EncodeTiledFn encode_tiled_entry() {
 
 int encode_tensor_map(CUtensorMap* map, const void* base, CUtensorMapDataType type, int element_bytes, int64_t cols,
                       int64_t heads, int64_t rows, int64_t batch, int64_t head_stride, int64_t row_stride,
-                      int64_t batch_stride, int box_cols, int box_rows) {
+                      int64_t batch_stride, int box_cols, int box_rows, int box_heads) {
   EncodeTiledFn encode = encode_tiled_entry();
   if (!encode) {
     set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
@@ -55,7 +55,7 @@ int encode_tensor_map(CUtensorMap* map, const void* base, CUtensorMapDataType ty
   if (batch == 1) strides[2] = strides[1] * (cuuint64_t)rows > strides[0] * (cuuint64_t)heads
                                    ? strides[1] * (cuuint64_t)rows
                                    : strides[0] * (cuuint64_t)heads;
-  cuuint32_t box[4] = {(cuuint32_t)box_cols, 1u, (cuuint32_t)box_rows, 1u};
+  cuuint32_t box[4] = {(cuuint32_t)box_cols, (cuuint32_t)box_heads, (cuuint32_t)box_rows, 1u};
   cuuint32_t element_strides[4] = {1, 1, 1, 1};
   const CUtensorMapSwizzle swizzle =
       box_cols * element_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE;

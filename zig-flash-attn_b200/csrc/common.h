@@ -35,10 +35,11 @@ void set_error(const char* format, ...);
   } while (0)
 
 // 4-D tensor map over a (batch, row, head, column) tensor of `element_bytes`-wide elements with strides in elements.
-// Box = (box_cols, 1 head, box_rows, 1 batch); swizzle 128 B when box_cols * element_bytes == 128.
+// Box = (box_cols, box_heads, box_rows, 1 batch); swizzle 128 B when box_cols * element_bytes == 128. In shared memory
+// a box is laid out row-major as [row][head][column].
 int encode_tensor_map(CUtensorMap* map, const void* base, CUtensorMapDataType type, int element_bytes, int64_t cols,
                       int64_t heads, int64_t rows, int64_t batch, int64_t head_stride, int64_t row_stride,
-                      int64_t batch_stride, int box_cols, int box_rows);
+                      int64_t batch_stride, int box_cols, int box_rows, int box_heads = 1);
 
 Problem to_problem(const b200fa_problem& in);
 

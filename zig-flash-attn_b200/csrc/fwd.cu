@@ -5,7 +5,11 @@
 // packed (varlen) and inter-sequence problems because key blocks come from the KeyCursor of attn_index.h.
 //
 // One persistent CTA per SM; the CTAs draw work items from a global counter (TileQueue). A work item is 256 query rows
-// of one head (two 128-row MMA tiles, "stages").
+// of one head (two 128-row MMA tiles, "stages"), or, with packed query heads (fixed-length problems whose key heads
+// serve a power-of-two group of G query heads; the reference packs the same way, zig/m_block_work.zig:17-35), 256 / G
+// tokens of all G heads of one key head: the Q box of the TMA load then spans (128 / G tokens, G heads), which lands
+// in shared memory as rows ordered token-major, and a softmax thread derives its (token, head) from its row. Packed
+// items read each key block once for the whole group and, under a causal mask, see fewer masked blocks.
 // Warp roles: warps 0-3 softmax of stage 0, warps 4-7 softmax of stage 1 (one thread per query row, TMEM lane =
 // row), warp 8 issues tcgen05 MMAs, warp 9 issues TMA loads.
 //   S_i = Q_i K_j^T   SS-MMA 128x128xD  into TMEM columns [128 i, 128 i + 128)
@@ -143,7 +147,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         FwdTile t = decode_tile(p, tile / p.splits);
         if (!t.valid) continue;
         KeyCursor cur;
-        cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kFwdTileM, t.s.lq));
+        cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + (kFwdTileM >> p.pack_shift), t.s.lq));
         if (p.splits > 1) cur.restrict_to_share(tile % p.splits, p.splits);
         OtherBlock kb;
         if (!cur.next(&kb)) continue;
@@ -151,7 +155,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         ++q_count;
         load_tile(&map_q, smem_q, bar_q_full, t.head, t.s.q0 + t.m0, t.s.batch_coord);
         if (!load_kv(&map_k, t.kv_head, kb.row, t.s.batch_coord)) { ok = false; break; }
-        load_tile(&map_q, smem_q + Cfg::kTileBytes, bar_q_full + 8, t.head, t.s.q0 + t.m0 + kBlockM, t.s.batch_coord);
+        load_tile(&map_q, smem_q + Cfg::kTileBytes, bar_q_full + 8, t.head, t.s.q0 + t.m0 + (kBlockM >> p.pack_shift),
+                  t.s.batch_coord);
         for (;;) {
           if (!load_kv(&map_v, t.kv_head, kb.row, t.s.batch_coord)) { ok = false; break; }
           if (!cur.next(&kb)) break;
@@ -212,7 +217,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         FwdTile t = decode_tile(p, tile / p.splits);
         if (!t.valid) continue;
         KeyCursor cur;
-        cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kFwdTileM, t.s.lq));
+        cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + (kFwdTileM >> p.pack_shift), t.s.lq));
         if (p.splits > 1) cur.restrict_to_share(tile % p.splits, p.splits);
         OtherBlock kb;
         if (!cur.next(&kb)) continue;
@@ -290,9 +295,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     for (int tile; ok && (tile = tiles.pop_warp(popped, wctx)) >= 0;) {
       FwdTile t = decode_tile(p, tile / p.splits);
       if (!t.valid) continue;
-      const int row = t.m0 + stage * kBlockM + row_in_stage;  // row within the sequence
+      // Row within the sequence and head of this thread (packed heads: tile row = token << pack_shift | head of group).
+      const int tile_row = stage * kBlockM + row_in_stage;
+      const int row = t.m0 + (tile_row >> p.pack_shift);
+      const int head = t.head + (tile_row & ((1 << p.pack_shift) - 1));
       KeyCursor cur;
-      cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kFwdTileM, t.s.lq));
+      cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + (kFwdTileM >> p.pack_shift), t.s.lq));
       const int split = p.splits > 1 ? tile % p.splits : 0;
       if (p.splits > 1) cur.restrict_to_share(split, p.splits);
       const int band_lo = cur.band.lo(row), band_hi = cur.band.hi(row);
@@ -428,14 +436,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       // ---- epilogue: O / l -> BF16 -> global, lse
       const bool row_valid = row < t.s.lq;
       __nv_bfloat16* o_row = p.o + t.s.batch_coord * p.o_batch_stride + (int64_t)(t.s.q0 + row) * p.o_row_stride +
-                             (int64_t)t.head * p.o_head_stride;
-      float* lse_ptr = p.lse + t.s.batch_coord * p.lse_batch_stride + (int64_t)t.head * p.lse_head_stride + t.s.q0 + row;
+                             (int64_t)head * p.o_head_stride;
+      float* lse_ptr = p.lse + t.s.batch_coord * p.lse_batch_stride + (int64_t)head * p.lse_head_stride + t.s.q0 + row;
       // Split-KV: this share's normalised output (fp32) and log-sum-exp go to the partial buffers instead.
       float* o_part = nullptr;
       if (p.splits > 1) {
         const int64_t global_row = (int64_t)t.s.batch_coord * pr.seqlen_q + row;
-        o_part = p.o_partial + (((int64_t)split * p.partial_rows + global_row) * pr.heads_q + t.head) * p.head_dim;
-        lse_ptr = p.lse_partial + ((int64_t)split * pr.heads_q + t.head) * p.partial_rows + global_row;
+        o_part = p.o_partial + (((int64_t)split * p.partial_rows + global_row) * pr.heads_q + head) * p.head_dim;
+        lse_ptr = p.lse_partial + ((int64_t)split * pr.heads_q + head) * p.partial_rows + global_row;
       }
       if (tile_blocks == 0) {
         if (row_valid) {
@@ -543,6 +551,24 @@ int acquire_tile_counter(cudaStream_t stream, int** counter) {
 // The plan is a pure function of the shapes (it assumes the 148 SMs of a B200), so the workspace size it implies can be
 // computed without a device.
 constexpr int kPlanSms = 148;
+
+// log2 of the query heads packed into the rows of a work item of fwd_kernel (0 = no packing): fixed-length problems
+// whose query heads per key head are a power of two between 2 and 128. B200FA_PACK_GQA=0 in the environment turns it off
+// (tuning comparisons). A pure function of the shapes, like the split plan that builds on it.
+static int pack_shift_of(const b200fa_problem& bp) {
+  static const bool disabled = [] {
+    const char* value = getenv("B200FA_PACK_GQA");
+    return value && value[0] == '0';
+  }();
+  if (disabled || bp.cu_seqlens_q || bp.visibility_bits || bp.head_dim > 128 || bp.heads_kv <= 0) return 0;
+  if (bp.heads_q % bp.heads_kv) return 0;
+  const int group = bp.heads_q / bp.heads_kv;
+  if (group < 2 || group > kBlockM || (group & (group - 1))) return 0;
+  int shift = 0;
+  while ((1 << shift) < group) ++shift;
+  return shift;
+}
+
 struct SplitPlan {
   int splits;
   size_t o_bytes, lse_bytes;
@@ -550,10 +576,11 @@ struct SplitPlan {
 static SplitPlan plan_split(const b200fa_problem& bp) {
   SplitPlan plan{1, 0, 0};
   if (bp.cu_seqlens_q || bp.visibility_bits || bp.head_dim > 128 || bp.batch <= 0 || bp.seqlen_q <= 0) return plan;
-  const int64_t tiles = (int64_t)bp.batch * bp.heads_q * ceil_div(bp.seqlen_q, kFwdTileM);
+  const int tile_tokens = kFwdTileM >> pack_shift_of(bp);
+  const int64_t tiles = (int64_t)bp.batch * (bp.heads_q >> pack_shift_of(bp)) * ceil_div(bp.seqlen_q, tile_tokens);
   int64_t keys = bp.seqlen_k;
   if (bp.window_left >= 0) {
-    const int64_t reach = (int64_t)bp.window_left + imin(bp.seqlen_q, kFwdTileM) + imax(bp.window_right, 0);
+    const int64_t reach = (int64_t)bp.window_left + imin(bp.seqlen_q, tile_tokens) + imax(bp.window_right, 0);
     keys = keys < reach ? keys : reach;
   }
   const int64_t blocks = (keys + kBlockN - 1) / kBlockN;
@@ -614,7 +641,7 @@ __global__ void __launch_bounds__(256) split_combine_kernel(const float* __restr
 
 int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim, int tile_rows, int kv_box_rows,
                     FwdParams* params, CUtensorMap* map_q, CUtensorMap* map_k, CUtensorMap* map_v, bool* nothing_to_do,
-                    int v_box_rows) {
+                    int v_box_rows, int pack_shift) {
   const b200fa_problem& bp = a.problem;
   const int D = bp.head_dim;  // columns of the tensors; `head_dim` is the width the kernel is compiled for
   (void)head_dim;
@@ -635,6 +662,7 @@ int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim,
   p.o_partial = nullptr;
   p.lse_partial = nullptr;
   p.partial_rows = 0;
+  p.pack_shift = packed ? 0 : pack_shift;
   p.tile_counter = nullptr;
   p.m_blocks = 0;
   p.head_dim = bp.head_dim;
@@ -656,14 +684,14 @@ int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim,
     p.work_list = static_cast<const int2*>(a.workspace);
     p.num_tiles = (int)(entries * bp.heads_q);
   } else {
-    p.m_blocks = ceil_div(bp.seqlen_q, tile_rows);
-    p.num_tiles = p.m_blocks * bp.batch * bp.heads_q;
+    p.m_blocks = ceil_div(bp.seqlen_q, tile_rows >> p.pack_shift);
+    p.num_tiles = p.m_blocks * bp.batch * (bp.heads_q >> p.pack_shift);
   }
   if (p.num_tiles <= 0 || rows_q == 0) return B200FA_OK;
 
   int status = encode_tensor_map(map_q, a.q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, bp.heads_q, rows_q, tensor_batch,
                                  a.q_stride[2], a.q_stride[1], packed ? rows_q * a.q_stride[1] : a.q_stride[0], 64,
-                                 kBlockM);
+                                 kBlockM >> p.pack_shift, 1 << p.pack_shift);
   if (status != B200FA_OK) return status;
   // An empty key tensor still needs valid maps: give them one row of the query tensor (never read, no key blocks).
   const bool no_keys = rows_k == 0;
@@ -691,7 +719,8 @@ static int launch_fwd_d(const b200fa_fwd_args& a, cudaStream_t stream) {
   FwdParams p;
   CUtensorMap map_q, map_k, map_v;
   bool nothing_to_do = false;
-  int status = prepare_forward(a, stream, D, kFwdTileM, kBlockN, &p, &map_q, &map_k, &map_v, &nothing_to_do);
+  int status = prepare_forward(a, stream, D, kFwdTileM, kBlockN, &p, &map_q, &map_k, &map_v, &nothing_to_do, 0,
+                               pack_shift_of(a.problem));
   if (status != B200FA_OK || nothing_to_do) return status;
   static bool attribute_set[64] = {false};
   status = set_dynamic_smem_once(reinterpret_cast<const void*>(&fwd_kernel<D>), Cfg::kSmemBytes, attribute_set);

@@ -25,6 +25,10 @@ struct FwdParams {
   float* o_partial;       // (splits, rows, heads_q, head_dim) fp32, rows = batch * seqlen_q
   float* lse_partial;     // (splits, heads_q, rows) fp32
   int64_t partial_rows;
+  // Packed query heads (fwd.cu, fixed-length problems with a power-of-two number of query heads per key head): the rows
+  // of a work item are (token, head of the group) pairs, row = token << pack_shift | head, so a work item covers
+  // 256 >> pack_shift tokens of all heads of one key head. 0: a work item is 256 tokens of one head.
+  int pack_shift;
 };
 
 struct FwdTile {
@@ -103,14 +107,15 @@ __device__ __forceinline__ FwdTile decode_tile(const FwdParams& p, int tile, int
     // Work items that run at the same time share K and V: all query blocks and query heads of one (batch entry, key
     // head) are consecutive, late (heavy under a causal mask) query blocks first, so the K/V stream they read stays
     // in L2 (reference zig/tile_scheduler.zig:516-669 orders tiles in L2-sized sections for the same reason).
-    const int group = pr.heads_q / pr.heads_kv;
+    const int ratio = pr.heads_q / pr.heads_kv;
+    const int group = p.pack_shift ? 1 : ratio;  // work items per query block and key head
     const int per_group = p.m_blocks * group;
     const int kv_group = tile / per_group;  // (batch entry, key head)
     const int rem = tile - kv_group * per_group;
     const int mb = rem / group;
     t.seq = kv_group / pr.heads_kv;
-    t.head = (kv_group - t.seq * pr.heads_kv) * group + (rem - mb * group);
-    t.m0 = (p.m_blocks - 1 - mb) * tile_rows;
+    t.head = (kv_group - t.seq * pr.heads_kv) * ratio + (rem - mb * group);  // packed: the first head of the group
+    t.m0 = (p.m_blocks - 1 - mb) * (tile_rows >> p.pack_shift);
     t.valid = true;
   }
   t.kv_head = t.head / (pr.heads_q / pr.heads_kv);
@@ -123,7 +128,8 @@ __device__ __forceinline__ FwdTile decode_tile(const FwdParams& p, int tile, int
 // needed. Defined in fwd.cu.
 int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim, int tile_rows, int kv_box_rows,
                     FwdParams* p, CUtensorMap* map_q, CUtensorMap* map_k, CUtensorMap* map_v, bool* nothing_to_do,
-                    int v_box_rows = 0 /* rows per TMA box of V when they differ from those of K */);
+                    int v_box_rows = 0 /* rows per TMA box of V when they differ from those of K */,
+                    int pack_shift = 0 /* log2 of the query heads packed into the rows of a work item */);
 // A zeroed work-item counter for one launch on `stream`: the next slot of the device's ring of 4096 counters inside the
 // library, reset by a memset node ahead of the kernel. Launches share a slot only 4096 launches apart (or through a
 // captured graph, which keeps its slot); see the contract at its definition in fwd.cu.
