@@ -114,6 +114,17 @@ size_t b200fa_bwd_workspace_bytes(const b200fa_problem* problem);
  * postprocess. dQ accumulates with floating-point atomics (not deterministic), as in the reference. */
 int b200fa_bwd(const b200fa_bwd_args* args, void* stream);
 
+/* Pivot gradients (the backward half of the reference's "softmax fix": zig/fragments.zig:23-30,
+ * zig/flash_bwd_sm100.zig:635-645,984-997, zig/flash_bwd_postprocess.zig:150-397). With the setting on, b200fa_bwd
+ * treats a key that holds more than 3/4 of the probability of a query row as the pivot of that row: its dS is not formed
+ * as P (dP - D), which cancels for P near 1, but as minus the sum of the BF16 dS of the other keys of the row, and the
+ * pivot terms of dQ and dK are added by the postprocess kernels. The results of rows without a pivot do not change.
+ * The setting is process-wide, read at every b200fa_bwd call; it starts as 1 when the environment variable
+ * B200FA_PIVOT_DS is "1" and as 0 otherwise (the pivot path costs the backward main kernel about 16 %; without it the
+ * gradients stay within the stated tolerance of the BF16 reference). Returns the previous value; a negative `enabled`
+ * only queries. The head_dim 256 kernel has no pivot path. */
+int b200fa_set_pivot_ds(int enabled);
+
 /* Measurement hook (no counterpart in the reference): the next b200fa_bwd call of the calling thread records the four
  * cudaEvent_t handles events[0..3] on its stream -- before the preprocess kernel, before the main kernel, after the
  * main kernel, after the postprocess kernel -- so a benchmark can time the main kernel by itself. NULL clears it. */

@@ -50,13 +50,26 @@ def test_workspace_sizes_are_shape_functions():
     assert library.b200fa_fwd_workspace_bytes(ctypes.byref(fixed)) == 0
     rows = 2 * 512
     stats = 8 * rows * 4
-    assert library.b200fa_bwd_workspace_bytes(ctypes.byref(fixed)) == 2 * stats + 8 * rows * 128 * 4
+    # lse_log2, dpsum, pivot_sum, pivot_key; the FP32 dQ accumulator; the flag block and the FP32 pivot terms of dK
+    key_rows = 2 * 512
+    assert library.b200fa_bwd_workspace_bytes(ctypes.byref(fixed)) == (
+        4 * stats + 8 * rows * 128 * 4 + 256 + 2 * key_rows * 128 * 4)
     packed = problem(batch=3, seqlen_q=1000, seqlen_k=900, cu_seqlens_q=8, cu_seqlens_k=8)
     entries = library.b200fa_work_list_entries(1000, 3, 256)
     assert entries == (1000 + 3 * 255) // 256
     assert library.b200fa_fwd_workspace_bytes(ctypes.byref(packed)) == entries * 8
     assert library.b200fa_work_list_entries(5, 10, 256) == 5
     assert library.b200fa_work_list_entries(0, 4, 256) == 0
+
+
+def test_pivot_setting_round_trips():
+    library = lib.library()
+    before = library.b200fa_set_pivot_ds(-1)
+    assert before in (0, 1)
+    assert library.b200fa_set_pivot_ds(1) == before
+    assert library.b200fa_set_pivot_ds(-1) == 1
+    assert library.b200fa_set_pivot_ds(before) == 1
+    assert library.b200fa_set_pivot_ds(-1) == before
 
 
 def test_invalid_arguments_report_errors_without_a_gpu():

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import attention_oracle as oracle
-from golden.make_golden import CASES, INTERSEQ, VARLEN, inputs
+from golden.make_golden import CASES, INTERSEQ, STABLE, STABLE_FIELDS, VARLEN, inputs, sharp_inputs
 
 GOLDEN = np.load(Path(__file__).parent / "golden" / "attention_golden.npz")
 
@@ -35,6 +35,26 @@ def test_attention_matches_reference_float64(seed_case):
     # float32 math (the arithmetic of the CPU baseline) stays within 1e-4 of float64
     out32, lse32, *_ = oracle.gradients(oracle.attention, q, k, v, dout, window_size=window, dtype=torch.float32)
     assert (out32.double() - out).abs().max() < 1e-4
+
+
+@pytest.mark.parametrize("seed_case", list(enumerate(STABLE)), ids=[case[0] for case in STABLE])
+def test_stable_attention_matches_reference_float64(seed_case):
+    """Every field of the float64 reference with the top key taken apart (out, lse, gradients, pivot rows, margins, error
+    weights) on inputs sharp enough that about half of the rows have a pivot."""
+    seed, (name, batch, sq, sk, hq, hkv, d, window, factor) = seed_case
+    q, k, v, dout = sharp_inputs(seed, batch, sq, sk, hq, hkv, d, factor)
+    mask = oracle.visible_keys([sq], [sk], sq, sk, window)[0]
+    for b in range(batch):
+        result = oracle.stable_attention(q[b], k[b], v[b], dout[b], mask)
+        for field in STABLE_FIELDS:
+            expected = torch.from_numpy(GOLDEN[f"{name}/{field}"][b])
+            value = result[field]
+            assert value.shape == expected.shape, field
+            if value.dtype == torch.bool:
+                assert torch.equal(value, expected.bool()), field
+            else:
+                assert torch.allclose(value.double(), expected, rtol=1e-9, atol=1e-12, equal_nan=True), field
+    assert 0.3 < float(torch.from_numpy(GOLDEN[f"{name}/pivot"]).mean()) < 0.9
 
 
 @pytest.mark.parametrize("index", range(len(VARLEN)))

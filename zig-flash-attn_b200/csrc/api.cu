@@ -1,5 +1,6 @@
 // C-ABI entry points (include/b200fa.h): argument validation, workspace sizing and dispatch to the launchers.
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 
 #include "common.h"
@@ -148,6 +149,15 @@ static int validate_problem(const b200fa_problem& p) {
 
 static bool strides_ok(const int64_t* stride) { return stride[0] % 8 == 0 && stride[1] % 8 == 0 && stride[2] % 8 == 0; }
 
+std::atomic<int>& pivot_setting() {
+  static std::atomic<int> value([] {
+    const char* env = getenv("B200FA_PIVOT_DS");
+    return env && env[0] == '1' ? 1 : 0;
+  }());
+  return value;
+}
+bool pivot_ds_enabled() { return pivot_setting().load(std::memory_order_relaxed) != 0; }
+
 }  // namespace b200fa
 
 using namespace b200fa;
@@ -198,6 +208,11 @@ int b200fa_fwd(const b200fa_fwd_args* args, void* stream) {
 int b200fa_set_trace(void* counters) {
   g_trace.store(static_cast<long long*>(counters), std::memory_order_relaxed);
   return B200FA_OK;
+}
+
+int b200fa_set_pivot_ds(int enabled) {
+  if (enabled < 0) return pivot_setting().load(std::memory_order_relaxed);
+  return pivot_setting().exchange(enabled ? 1 : 0, std::memory_order_relaxed);
 }
 
 int b200fa_bwd_timing_events(void* const* events) {

@@ -68,7 +68,7 @@ struct BwdConfig {
   static constexpr int kTmemS = 0, kTmemDp = 128, kTmemDv = 256, kTmemDk = 256 + D;
 };
 
-template <int D>
+template <int D, bool kPivot>
 __global__ void __launch_bounds__(BwdConfig<D>::kThreads, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
            const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
@@ -109,7 +109,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   const uint32_t bar_kv_full = bars, bar_q_full = bars + 8 /*[2]*/, bar_q_empty = bars + 24 /*[2]*/;
   const uint32_t bar_do_full = bars + 40, bar_s_full = bars + 56, bar_p_full = bars + 64;
   const uint32_t bar_dp_full = bars + 72, bar_ds_full = bars + 80, bar_dq_full = bars + 88, bar_dq_empty = bars + 96;
-  const uint32_t bar_final = bars + 104;
+  const uint32_t bar_final = bars + 104, bar_ds_free = bars + 120;
   const uint32_t tmem_slot = bars + 112, abort_slot = bars + 116;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + (abort_slot - smem_u32(smem_raw)));
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
@@ -135,6 +135,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     mbar_init(bar_dq_full, 1);
     mbar_init(bar_dq_empty, 128 * Cfg::kDrains);
     mbar_init(bar_final, 1);
+    mbar_init(bar_ds_free, 128 * Cfg::kDrains);
     fence_barrier_init();
   }
   constexpr int kMmaWarp = Cfg::kComputeWarps + 4 * Cfg::kDrains, kLoadWarp = kMmaWarp + 1;
@@ -383,6 +384,26 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar_p_full);
+        // A probability above 3/4 is the pivot of its query row: dV keeps it (P^T is stored above), dS leaves it out
+        // and the postprocess kernel forms it from the sum of the others. The branch is uniform over the warp and
+        // almost never taken.
+        if constexpr (kPivot) {
+          // Necessary for a probability above 3/4 among the thread's C: their sum is above 3/4 (packed adds).
+          float2 total = make_float2(pf[0], pf[1]);
+#pragma unroll
+          for (int j = 2; j < C; j += 2) total = __fadd2_rn(total, make_float2(pf[j], pf[j + 1]));
+          if (__any_sync(0xffffffffu, total.x + total.y > kPivotProbability)) {
+            const int head = kv_head * group + g;
+            int* keys = p.pivot_key + (int64_t)head * p.rows + stat_base + qb.row + cb;
+#pragma unroll
+            for (int j = 0; j < C; ++j) {
+              if (pf[j] > kPivotProbability) {
+                keys[j] = s.k0 + c;
+                pf[j] = 0.f;
+              }
+            }
+          }
+        }
         trace_add(wctx, 13, trace_clock(wctx) - t_p);
         trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 600 + it);  // P stored
         trace_event(wctx, traced_cta && threadIdx.x == 32 * Cfg::kComputeWarps - 32 && it < 10, 4, trace_n, 1600 + it);  // the same from the last compute warp
@@ -390,6 +411,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         if (!mbar_wait_traced(bar_dp_full, it & 1, wctx, kWaitBwdCompute, 8, true)) { ok = false; break; }
         // The dS tile of the previous iteration must have been consumed by its dK and dQ MMAs.
         if (it > 0 && !mbar_wait_traced(bar_q_empty + 8 * ((it - 1) & 1), ((it - 1) >> 1) & 1, wctx, kWaitBwdCompute, 9, true)) { ok = false; break; }
+        // ... and summed over its keys by the drain warps (pivot rows).
+        if (kPivot && it > 0 && !mbar_wait_traced(bar_ds_free, (it - 1) & 1, wctx, kWaitBwdCompute, 16, true)) { ok = false; break; }
         tc_fence_after();
         const long long t_ds = trace_clock(wctx);
         trace_event(wctx, traced_cta && threadIdx.x == 0 && it < 10, 1, trace_n, 700 + it);  // dP ready
@@ -531,6 +554,67 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           }
           ++chunks;
         }
+        // Sums of the BF16 dS over the 128 keys of the block, per query row, after the drain, off the chain dS -> dQ ->
+        // drain -> next dP^T (placed before the drain they cost the kernel 10 %). Drain warp w takes
+        // the 16-byte chunks (8 queries) c0 and c0 + 1 of the [key][query] tile: lane = (key row mod 16, chunk), eight
+        // loads cover the 128 rows (a warp-wide load reads 16 rows x 32 bytes, 4 wavefronts of 128 bytes: no excess bank
+        // conflicts under the tile's swizzle), FP32 adds in packed pairs, then a halving exchange over the 16 row lanes
+        // leaves one query's sum per lane. (A warp-level mma.sync with an all-ones A costs 10 % of the kernel: it
+        // costs the same.) The compute warps overwrite the tile only after bar_ds_free, which the drain warps arrive at below.
+        if (kPivot && !mbar_wait_traced(bar_ds_full, it & 1, wctx, kWaitBwdReduce, 15, true)) { ok = false; break; }
+        if constexpr (kPivot) {
+          constexpr int kRounds = 8 / (4 * Cfg::kDrains);  // pairs of chunks per drain warp (16 chunks in all)
+          const int drain_warp = warp - Cfg::kComputeWarps;
+          const int sel = lane & 1, row_lane = lane >> 1;
+          float sums[kRounds];
+#pragma unroll
+          for (int round = 0; round < kRounds; ++round) {
+            const int chunk = 2 * (drain_warp * kRounds + round) + sel;  // queries [8 chunk, 8 chunk + 8)
+            const uint32_t panel = smem_ds + (chunk >> 3) * Cfg::kPanelBytes;
+            float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int key = 16 * i + row_lane;
+              const float4 w = ld_shared_f4(panel + key * 128 + (((chunk & 7) ^ (key & 7)) << 4));
+              const uint32_t words[4] = {__float_as_uint(w.x), __float_as_uint(w.y), __float_as_uint(w.z), __float_as_uint(w.w)};
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                acc[j] = __fadd2_rn(acc[j], make_float2(__uint_as_float(words[j] << 16), __uint_as_float(words[j] & 0xffff0000u)));
+            }
+            // Halving exchange over lane bits 4, 3, 2 (each step keeps one half of the values and adds the partner's),
+            // then a plain exchange over bit 1: the lane ends with the sum of query 4 b4 + 2 b3 + b2 of its chunk.
+            float v[8] = {acc[0].x, acc[0].y, acc[1].x, acc[1].y, acc[2].x, acc[2].y, acc[3].x, acc[3].y};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const bool upper = lane & 16;
+              const float send = upper ? v[k] : v[k + 4], keep = upper ? v[k + 4] : v[k];
+              v[k] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+            }
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+              const bool upper = lane & 8;
+              const float send = upper ? v[k] : v[k + 2], keep = upper ? v[k + 2] : v[k];
+              v[k] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+            }
+            {
+              const bool upper = lane & 4;
+              const float send = upper ? v[0] : v[1], keep = upper ? v[1] : v[0];
+              v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+            }
+            v[0] += __shfl_xor_sync(0xffffffffu, v[0], 2);
+            sums[round] = v[0];
+          }
+          // The tile may be overwritten from here on. The arrive comes before the reductions: it has release
+          // semantics, and behind them it would wait for their round trip to L2 (measured: 12 % of the kernel).
+          mbar_arrive(bar_ds_free);
+#pragma unroll
+          for (int round = 0; round < kRounds; ++round) {
+            const int chunk = 2 * (drain_warp * kRounds + round) + sel;
+            const int q = 8 * chunk + ((lane >> 2) & 7);  // 4 b4 + 2 b3 + b2
+            if ((lane & 2) == 0 && sums[round] != 0.f && row0 + q < p.rows)
+              red_add_f32(p.pivot_sum + (int64_t)head * p.rows + row0 + q, sums[round] * kPivotSumScale);
+          }
+        }
         ++it;
       }
     }
@@ -580,12 +664,14 @@ struct PrePost {
   static constexpr int kRowsPerBlock = 8 * kRowsPerWarp;
 };
 
-// dpsum = -sum_d O dO, lse_log2 = -lse log2(e), dq_accum row = 0 (reference zig/flash_bwd_preprocess.zig:118-237).
+// dpsum = -sum_d O dO, lse_log2 = -lse log2(e), dq_accum row = 0, no pivot yet (reference
+// zig/flash_bwd_preprocess.zig:118-237).
 template <int D>
 __global__ void __launch_bounds__(256) bwd_preprocess_kernel(
     const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout, const float* __restrict__ lse,
     int64_t o_bs, int64_t o_rs, int64_t o_hs, int64_t do_bs, int64_t do_rs, int64_t do_hs, int64_t lse_bs, int64_t lse_hs,
-    RowMap map, int heads, float* __restrict__ lse_log2, float* __restrict__ dpsum, float* __restrict__ dq_accum) {
+    RowMap map, int heads, float* __restrict__ lse_log2, float* __restrict__ dpsum, float* __restrict__ dq_accum,
+    float* __restrict__ pivot_sum, int* __restrict__ pivot_key) {
   using P = PrePost<D>;
   const int lane = threadIdx.x & 31;
   const int sub = lane % P::kLanesPerRow;  // 8-column group of the row
@@ -612,17 +698,35 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(
     const float value = lse[batch_coord * lse_bs + (int64_t)head * lse_hs + tensor_row];
     lse_log2[stat] = value == -INFINITY ? -INFINITY : -value * kLog2e;  // rows without keys: exp2(x + -inf) = 0
     dpsum[stat] = -sum;
+    pivot_sum[stat] = 0.f;
+    pivot_key[stat] = -1;
   }
   float4* acc = reinterpret_cast<float4*>(dq_accum + stat * D + sub * 8);
   acc[0] = make_float4(0.f, 0.f, 0.f, 0.f);
   acc[1] = make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
-// dq = bf16(scale * dq_accum) for valid rows (reference zig/flash_bwd_postprocess.zig:139-347).
+// The pivot terms that the postprocess kernel adds (all null / zero: none).
+struct PivotFix {
+  const float* pivot_sum;        // (heads_q, rows): kPivotSumScale x the sum of the BF16 dS of the other keys of the row
+  const int* pivot_key;          // (heads_q, rows): tensor row of the pivot key, -1 = the row has none
+  const __nv_bfloat16* q;        // query and key tensors, for the two products with the dS of the pivot
+  const __nv_bfloat16* k;
+  int64_t q_bs, q_rs, q_hs, k_bs, k_rs, k_hs;
+  float* dk_fix;                 // (heads_kv, key rows, D) FP32, kDkFixScale x the pivot terms of dK, zeroed beforehand
+  int* any_pivot;                // set to 1 when some row has a pivot
+  int64_t key_rows;              // key rows per batch entry (seqlen_k), or of the packed tensor
+  int group;                     // query heads per key head
+};
+
+// dq = bf16(scale * (dq_accum + dS_pivot * K[pivot])) for valid rows, and the pivot term dS_pivot * scale * Q[row] of
+// dK into the FP32 side buffer (reference zig/flash_bwd_postprocess.zig:139-347). dS_pivot = -pivot_sum / kPivotSumScale:
+// the dS of a row add up to zero, so the one the main kernel left out is minus the sum of the others, without the
+// cancellation of P (dP - D) for P near 1 (reference zig/fragments.zig:23-30).
 template <int D>
 __global__ void __launch_bounds__(256) bwd_postprocess_kernel(const float* __restrict__ dq_accum, RowMap map, float scale,
                                                               __nv_bfloat16* __restrict__ dq, int64_t dq_bs,
-                                                              int64_t dq_rs, int64_t dq_hs) {
+                                                              int64_t dq_rs, int64_t dq_hs, PivotFix fix) {
   using P = PrePost<D>;
   const int lane = threadIdx.x & 31;
   const int sub = lane % P::kLanesPerRow;
@@ -632,14 +736,74 @@ __global__ void __launch_bounds__(256) bwd_postprocess_kernel(const float* __res
   int batch_coord;
   int64_t tensor_row;
   if (!locate_row(map, row, &batch_coord, &tensor_row)) return;
-  const float4* acc = reinterpret_cast<const float4*>(dq_accum + ((int64_t)head * map.rows + row) * D + sub * 8);
-  const float4 v = acc[0], w = acc[1];
+  const int64_t stat = (int64_t)head * map.rows + row;
+  const float4* acc = reinterpret_cast<const float4*>(dq_accum + stat * D + sub * 8);
+  float4 v = acc[0], w = acc[1];
+  const int key = fix.pivot_key ? fix.pivot_key[stat] : -1;
+  if (key >= 0) {
+    const float ds = fix.pivot_sum[stat] * (-1.f / kPivotSumScale);
+    const int kv_head = head / fix.group;
+    const uint4 kw = *reinterpret_cast<const uint4*>(fix.k + batch_coord * fix.k_bs + (int64_t)key * fix.k_rs +
+                                                     (int64_t)kv_head * fix.k_hs + sub * 8);
+    const uint4 qw = *reinterpret_cast<const uint4*>(fix.q + batch_coord * fix.q_bs + tensor_row * fix.q_rs +
+                                                     (int64_t)head * fix.q_hs + sub * 8);
+    const uint32_t kk[4] = {kw.x, kw.y, kw.z, kw.w}, qq[4] = {qw.x, qw.y, qw.z, qw.w};
+    float dqv[8] = {v.x, v.y, v.z, v.w, w.x, w.y, w.z, w.w};
+    float* side = fix.dk_fix + (((int64_t)kv_head * (map.cu_q ? 1 : map.batch) + batch_coord) * fix.key_rows + key) * D + sub * 8;
+    const float ds_scaled = ds * kDkFixScale;  // exact: a power of two, and the product stays normal
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float k_lo = __uint_as_float(kk[i] << 16), k_hi = __uint_as_float(kk[i] & 0xffff0000u);
+      const float q_lo = __uint_as_float(qq[i] << 16), q_hi = __uint_as_float(qq[i] & 0xffff0000u);
+      dqv[2 * i] = fmaf(ds, k_lo, dqv[2 * i]);
+      dqv[2 * i + 1] = fmaf(ds, k_hi, dqv[2 * i + 1]);
+      const float t_lo = ds_scaled * (scale * q_lo), t_hi = ds_scaled * (scale * q_hi);
+      if (t_lo != 0.f) red_add_f32(side + 2 * i, t_lo);
+      if (t_hi != 0.f) red_add_f32(side + 2 * i + 1, t_hi);
+    }
+    v = make_float4(dqv[0], dqv[1], dqv[2], dqv[3]);
+    w = make_float4(dqv[4], dqv[5], dqv[6], dqv[7]);
+    if (sub == 0) *fix.any_pivot = 1;
+  }
   uint4 packed;
   packed.x = pack_bf16x2(v.x * scale, v.y * scale);
   packed.y = pack_bf16x2(v.z * scale, v.w * scale);
   packed.z = pack_bf16x2(w.x * scale, w.y * scale);
   packed.w = pack_bf16x2(w.z * scale, w.w * scale);
   *reinterpret_cast<uint4*>(dq + batch_coord * dq_bs + tensor_row * dq_rs + (int64_t)head * dq_hs + sub * 8) = packed;
+}
+
+// dk += the pivot terms gathered by the postprocess kernel (reference zig/flash_bwd_postprocess.zig:349-397): the main
+// kernel wrote dk without them, rounded to BF16; keys without a term stay untouched. The whole kernel is a no-op when
+// no row had a pivot.
+template <int D>
+__global__ void __launch_bounds__(256) bwd_fix_dk_kernel(const float* __restrict__ dk_fix, const int* __restrict__ any_pivot,
+                                                         int64_t rows, int64_t key_rows, int heads_kv, int head_dim,
+                                                         __nv_bfloat16* __restrict__ dk, int64_t dk_bs, int64_t dk_rs,
+                                                         int64_t dk_hs) {
+  if (*any_pivot == 0) return;
+  constexpr int kLanes = D / 8;
+  const int64_t items = rows * heads_kv * kLanes;  // rows = key rows of all batch entries
+  for (int64_t item = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; item < items; item += (int64_t)gridDim.x * blockDim.x) {
+    const int sub = (int)(item % kLanes);
+    const int64_t flat = item / kLanes;  // kv_head * rows + row
+    const int kv_head = (int)(flat / rows);
+    const int64_t row = flat - (int64_t)kv_head * rows;
+    if (sub * 8 >= head_dim) continue;
+    const float4* src = reinterpret_cast<const float4*>(dk_fix + flat * D + sub * 8);
+    const float4 a = src[0], b = src[1];
+    if (a.x == 0.f && a.y == 0.f && a.z == 0.f && a.w == 0.f && b.x == 0.f && b.y == 0.f && b.z == 0.f && b.w == 0.f) continue;
+    const int64_t batch_coord = row / key_rows, key = row - batch_coord * key_rows;
+    uint4* dst = reinterpret_cast<uint4*>(dk + batch_coord * dk_bs + key * dk_rs + (int64_t)kv_head * dk_hs + sub * 8);
+    const uint4 old = *dst;
+    const float unscale = 1.f / kDkFixScale;
+    uint4 packed;
+    packed.x = pack_bf16x2(__uint_as_float(old.x << 16) + a.x * unscale, __uint_as_float(old.x & 0xffff0000u) + a.y * unscale);
+    packed.y = pack_bf16x2(__uint_as_float(old.y << 16) + a.z * unscale, __uint_as_float(old.y & 0xffff0000u) + a.w * unscale);
+    packed.z = pack_bf16x2(__uint_as_float(old.z << 16) + b.x * unscale, __uint_as_float(old.z & 0xffff0000u) + b.y * unscale);
+    packed.w = pack_bf16x2(__uint_as_float(old.w << 16) + b.z * unscale, __uint_as_float(old.w & 0xffff0000u) + b.w * unscale);
+    *dst = packed;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------- host side
@@ -655,8 +819,8 @@ static void mark(int index, cudaStream_t stream) {
 }
 
 struct BwdWorkspace {
-  size_t lse_log2, dpsum, dq_accum, work_list, total;
-  int64_t rows, entries;
+  size_t lse_log2, dpsum, pivot_sum, pivot_key, dq_accum, dk_fix, dk_fix_bytes, work_list, total;
+  int64_t rows, key_rows, entries;
 };
 
 static BwdWorkspace plan_workspace(const b200fa_problem& p) {
@@ -666,10 +830,17 @@ static BwdWorkspace plan_workspace(const b200fa_problem& p) {
   const size_t stat_bytes = ((size_t)p.heads_q * w.rows * 4 + 255) & ~size_t(255);
   w.lse_log2 = 0;
   w.dpsum = stat_bytes;
-  w.dq_accum = 2 * stat_bytes;
+  w.pivot_sum = 2 * stat_bytes;
+  w.pivot_key = 3 * stat_bytes;
+  w.dq_accum = 4 * stat_bytes;
   const int compiled_dim = p.head_dim <= 64 ? 64 : p.head_dim <= 128 ? 128 : 256;  // the accumulator has the compiled width
   const size_t acc_bytes = ((size_t)p.heads_q * w.rows * compiled_dim * 4 + 255) & ~size_t(255);
-  w.work_list = w.dq_accum + acc_bytes;
+  // Pivot terms of dK (head_dim <= 128): 256 bytes that hold the "some row has a pivot" flag, then
+  // (heads_kv, key rows, compiled width) FP32; one memset zeroes both.
+  w.key_rows = packed ? (int64_t)p.seqlen_k : (int64_t)p.batch * p.seqlen_k;
+  w.dk_fix = w.dq_accum + acc_bytes;
+  w.dk_fix_bytes = compiled_dim <= 128 ? 256 + (((size_t)p.heads_kv * w.key_rows * compiled_dim * 4 + 255) & ~size_t(255)) : 0;
+  w.work_list = w.dk_fix + w.dk_fix_bytes;
   w.entries = packed ? work_list_entries(p.seqlen_k, p.batch, kBlockN) : 0;
   w.total = w.work_list + (size_t)w.entries * 8;
   return w;
@@ -715,10 +886,17 @@ static int launch_main(const b200fa_bwd_args& a, const BwdParams& p, dim3 grid, 
     if (status != B200FA_OK) return status;
   }
 
-  static bool attribute_set[64] = {false};
-  status = set_dynamic_smem_once(reinterpret_cast<const void*>(&bwd_kernel<D>), Cfg::kSmemBytes, attribute_set);
-  if (status != B200FA_OK) return status;
-  bwd_kernel<D><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_q, map_k, map_v, map_do, map_dq, p);
+  if (p.pivot_key) {
+    static bool attribute_set[64] = {false};
+    status = set_dynamic_smem_once(reinterpret_cast<const void*>(&bwd_kernel<D, true>), Cfg::kSmemBytes, attribute_set);
+    if (status != B200FA_OK) return status;
+    bwd_kernel<D, true><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_q, map_k, map_v, map_do, map_dq, p);
+  } else {
+    static bool attribute_set[64] = {false};
+    status = set_dynamic_smem_once(reinterpret_cast<const void*>(&bwd_kernel<D, false>), Cfg::kSmemBytes, attribute_set);
+    if (status != B200FA_OK) return status;
+    bwd_kernel<D, false><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_q, map_k, map_v, map_do, map_dq, p);
+  }
   B200FA_CUDA_CHECK(cudaGetLastError());
 
   return B200FA_OK;
@@ -739,6 +917,12 @@ static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
   float* lse_log2 = reinterpret_cast<float*>(ws + w.lse_log2);
   float* dpsum = reinterpret_cast<float*>(ws + w.dpsum);
   float* dq_accum = reinterpret_cast<float*>(ws + w.dq_accum);
+  float* pivot_sum = reinterpret_cast<float*>(ws + w.pivot_sum);
+  int* pivot_key = reinterpret_cast<int*>(ws + w.pivot_key);
+  // Pivot gradients: on request (b200fa_set_pivot_ds); the head_dim 256 kernel has no pivot handling.
+  const bool pivots = pivot_ds_enabled() && w.dk_fix_bytes > 0 && w.rows > 0 && w.key_rows > 0;
+  int* any_pivot = reinterpret_cast<int*>(ws + w.dk_fix);
+  float* dk_fix = reinterpret_cast<float*>(ws + w.dk_fix + 256);
   const int64_t tensor_batch = packed ? 1 : bp.batch;
 
   RowMap map{bp.cu_seqlens_q, bp.batch, bp.seqlen_q, w.rows, bp.head_dim};
@@ -748,9 +932,11 @@ static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
     bwd_preprocess_kernel<D><<<grid, 256, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(a.out), static_cast<const __nv_bfloat16*>(a.dout), a.softmax_lse,
         packed ? 0 : a.out_stride[0], a.out_stride[1], a.out_stride[2], packed ? 0 : a.dout_stride[0], a.dout_stride[1],
-        a.dout_stride[2], packed ? 0 : a.lse_stride[0], a.lse_stride[1], map, bp.heads_q, lse_log2, dpsum, dq_accum);
+        a.dout_stride[2], packed ? 0 : a.lse_stride[0], a.lse_stride[1], map, bp.heads_q, lse_log2, dpsum, dq_accum,
+        pivot_sum, pivot_key);
     B200FA_CUDA_CHECK(cudaGetLastError());
   }
+  if (pivots) B200FA_CUDA_CHECK(cudaMemsetAsync(ws + w.dk_fix, 0, w.dk_fix_bytes, stream));
 
   BwdParams p;
   p.prob = to_problem(bp);
@@ -759,6 +945,8 @@ static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
   p.lse_log2 = lse_log2;
   p.dpsum = dpsum;
   p.rows = w.rows;
+  p.pivot_sum = pivots ? pivot_sum : nullptr;
+  p.pivot_key = pivots ? pivot_key : nullptr;
   p.head_dim = bp.head_dim;
   p.dk = static_cast<__nv_bfloat16*>(a.dk);
   p.dv = static_cast<__nv_bfloat16*>(a.dv);
@@ -826,9 +1014,29 @@ static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
 
   if (w.rows > 0) {
     dim3 post((unsigned)((w.rows + PrePost<D>::kRowsPerBlock - 1) / PrePost<D>::kRowsPerBlock), (unsigned)bp.heads_q);
+    PivotFix fix{};
+    if (pivots && run_main) {
+      fix.pivot_sum = pivot_sum;
+      fix.pivot_key = pivot_key;
+      fix.q = static_cast<const __nv_bfloat16*>(a.q);
+      fix.k = static_cast<const __nv_bfloat16*>(a.k);
+      fix.q_bs = packed ? 0 : a.q_stride[0], fix.q_rs = a.q_stride[1], fix.q_hs = a.q_stride[2];
+      fix.k_bs = packed ? 0 : a.k_stride[0], fix.k_rs = a.k_stride[1], fix.k_hs = a.k_stride[2];
+      fix.dk_fix = dk_fix;
+      fix.any_pivot = any_pivot;
+      fix.key_rows = bp.seqlen_k;
+      fix.group = bp.heads_q / bp.heads_kv;
+    }
     bwd_postprocess_kernel<D><<<post, 256, 0, stream>>>(dq_accum, map, bp.softmax_scale, static_cast<__nv_bfloat16*>(a.dq),
-                                                        packed ? 0 : a.dq_stride[0], a.dq_stride[1], a.dq_stride[2]);
+                                                        packed ? 0 : a.dq_stride[0], a.dq_stride[1], a.dq_stride[2], fix);
     B200FA_CUDA_CHECK(cudaGetLastError());
+    if (pivots && run_main) {
+      const int64_t items = w.key_rows * bp.heads_kv * (D / 8);
+      const unsigned blocks = (unsigned)(items / 256 + 1 < 148 * 8 ? items / 256 + 1 : 148 * 8);
+      bwd_fix_dk_kernel<D><<<blocks, 256, 0, stream>>>(dk_fix, any_pivot, w.key_rows, bp.seqlen_k, bp.heads_kv, bp.head_dim,
+                                                       p.dk, p.dk_batch_stride, p.dk_row_stride, p.dk_head_stride);
+      B200FA_CUDA_CHECK(cudaGetLastError());
+    }
   }
   mark(3, stream);
   g_timing_armed = false;

@@ -8,6 +8,14 @@
 namespace b200fa {
 
 constexpr float kLog2e = 1.4426950408889634f;
+// The reference's rule (zig/fragments.zig:23-30): a key with a probability above 3/4 is the pivot of its row.
+constexpr float kPivotProbability = 0.75f;
+// Row sums of BF16 dS are multiples of 2^-133; scaled by 2^7 every nonzero sum is a normal FP32 number, which the
+// reductions (red.add.f32 flushes subnormal numbers) keep (reference zig/BackwardParams.zig:52-58).
+constexpr float kPivotSumScale = 128.f;
+// The pivot terms of dK are summed in FP32 by atomic adds, scaled by 2^40 for the same reason: a term as small as
+// 2^-166 stays normal, sums up to 2^87 stay finite.
+constexpr float kDkFixScale = 1099511627776.f;
 
 struct BwdParams {
   Problem prob;
@@ -15,6 +23,12 @@ struct BwdParams {
   const float* lse_log2;  // (heads_q, rows) : -lse * log2(e)
   const float* dpsum;     // (heads_q, rows) : -sum_d O * dO
   int64_t rows;           // rows of the statistics / dQ accumulator per head (batch * seqlen_q or total_q)
+  // Pivot rows (at most one key of a query row holds more than 3/4 of its probability): the main kernel leaves the dS
+  // of that key out, records the key in `pivot_key` (tensor row of K, -1 = none) and adds the BF16 dS of the other keys,
+  // times kPivotSumScale, into `pivot_sum`; the postprocess kernel takes the dS of the pivot as minus that sum. Both are
+  // (heads_q, rows). Null: the kernel has no pivot handling (head_dim 256).
+  float* pivot_sum;
+  int* pivot_key;
   int head_dim;           // columns of the tensors (<= the compiled D; TMA zero-fills the columns in between)
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;

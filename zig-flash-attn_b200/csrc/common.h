@@ -57,6 +57,8 @@ int set_dynamic_smem_once(const void* kernel, int bytes, bool (&done)[64]);
 // Device address of the library's status word on the current device (null + error text on failure).
 int* device_status_word();
 
+// The process-wide pivot-gradient setting (b200fa_set_pivot_ds).
+bool pivot_ds_enabled();
 // Device buffer of 32 cycle counters set with b200fa_set_trace (null = tracing off).
 long long* trace_buffer();
 

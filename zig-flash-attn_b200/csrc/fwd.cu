@@ -304,7 +304,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       const int split = p.splits > 1 ? tile % p.splits : 0;
       if (p.splits > 1) cur.restrict_to_share(split, p.splits);
       const int band_lo = cur.band.lo(row), band_hi = cur.band.hi(row);
+      // Row state: `m` is the lazy reference maximum, `l` the sum of the exponentials relative to it of every key except
+      // the keys set aside (TopApart, fwd_common.cuh: the tie-counting LSE of the reference,
+      // zig/flash_fwd_sm100.zig:885-901, with the counting done only in the blocks where it can matter).
       float m = -INFINITY, l = 0.f;
+      TopApart top;
       int tile_blocks = 0;
       OtherBlock kb;
       while (cur.next(&kb)) {
@@ -356,29 +360,45 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         tmem_ld32(t_s + 96, reinterpret_cast<uint32_t*>(high) + 32);
         tc_wait_ld();
         if (masked) apply_mask(high, 64);
-        const float m_new = fmaxf(m, fmaxf(max_low, max_of(high)));
+        const float max_high = max_of(high);
+        const float block_max = fmaxf(max_low, max_high);
+        const float m_new = fmaxf(m, block_max);
+        const bool set_apart = sets_keys_apart(top, max_low, max_high, scale_log2);
+        const bool counting = __any_sync(0xffffffffu, set_apart);
         trace_event(wctx, traced, 1 + stage, trace_n, 4000 + 1000 * stage + (tile_blocks % 100));  // row maximum known
         const bool grow = (m_new - m) * scale_log2 > 8.f;  // also true when m is -inf and m_new is finite
-        if (__any_sync(0xffffffffu, grow)) {
-          float alpha = 1.f;
-          if (grow) {
-            alpha = (m == -INFINITY) ? 0.f : ex2_approx((m - m_new) * scale_log2);
-            l *= alpha;
-            m = m_new;
-          }
-          if (tile_blocks > 0) {
-            // The scores of this block are present, so the PV product of the previous block has completed.
-            const float2 alpha2 = make_float2(alpha, alpha);
+        // One rarely taken branch holds both the rescale and the second summation of blocks with keys set aside, so the
+        // common path has a single branch between the maximum and the exponentials.
+        const bool any_grow = __any_sync(0xffffffffu, grow);
+        float sum_counted = 0.f;
+        if (any_grow || counting) {
+          if (any_grow) {
+            float alpha = 1.f;
+            if (grow) {
+              alpha = (m == -INFINITY) ? 0.f : ex2_approx((m - m_new) * scale_log2);
+              l *= alpha;
+              m = m_new;
+            }
+            if (tile_blocks > 0) {
+              // The scores of this block are present, so the PV product of the previous block has completed.
+              const float2 alpha2 = make_float2(alpha, alpha);
 #pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-              float2 o[16];
-              tmem_ld32(t_o + 32 * c, reinterpret_cast<uint32_t*>(o));
-              tc_wait_ld();
+              for (int c = 0; c < D / 32; ++c) {
+                float2 o[16];
+                tmem_ld32(t_o + 32 * c, reinterpret_cast<uint32_t*>(o));
+                tc_wait_ld();
 #pragma unroll
-              for (int i = 0; i < 16; ++i) o[i] = __fmul2_rn(o[i], alpha2);
-              tmem_st32(t_o + 32 * c, reinterpret_cast<uint32_t*>(o));
+                for (int i = 0; i < 16; ++i) o[i] = __fmul2_rn(o[i], alpha2);
+                tmem_st32(t_o + 32 * c, reinterpret_cast<uint32_t*>(o));
+              }
             }
           }
+          // Blocks in which some row of the warp sets keys aside (rare) sum their exponentials a second time, without
+          // those keys, here, where the rescale branch already splits the instruction stream: the common path below
+          // carries no compare per score.
+          if (counting)
+            sum_counted = sum_without_keys_apart<kBlockN>(top, l, set_apart, block_max, t_s, masked, lo, hi, scale_log2,
+                                                          (m == -INFINITY) ? 0.f : m * scale_log2);
         }
         const float mc = (m == -INFINITY) ? 0.f : m * scale_log2;
         const float2 scale2 = make_float2(scale_log2, scale_log2), shift2 = make_float2(-mc, -mc);
@@ -422,7 +442,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           if (masked) apply_mask(low, 0);
           exponentiate(low, 0);
         }
-        l += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
+        l += counting ? sum_counted : (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(my_p_full);
@@ -465,7 +485,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       ++tiles_done;
       const long long t_epi = trace_clock(wctx);
       tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      float total, lse_row;
+      row_totals(m, l, top.ones, top.apart, top.row_max, scale_log2, &total, &lse_row);
+      const float inv = total > 0.f ? 1.f / total : 0.f;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
@@ -490,10 +512,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           }
         }
       }
-      if (row_valid) {
-        const float mc = (m == -INFINITY) ? 0.f : m * scale_log2;
-        *lse_ptr = l > 0.f ? (mc + log2f(l)) * 0.69314718055994531f : -INFINITY;
-      }
+      if (row_valid) *lse_ptr = lse_row;
       tc_fence_before();
       trace_add(wctx, 23, trace_clock(wctx) - t_epi);
       trace_add(wctx, 24, 1);
@@ -615,28 +634,39 @@ __global__ void __launch_bounds__(256) split_combine_kernel(const float* __restr
   const int g = (int)(index % groups);
   const int head = (int)((index / groups) % heads);
   const int64_t row = index / groups / heads;
+  // The share with the largest log-sum-exp has the weight 1 exactly; the weights of the others are summed apart from
+  // it and enter the logarithm as log1p(rest), so a row whose log-sum-exp is close to zero keeps its relative accuracy
+  // across the shares (reference tests/test_softmax_fix.py:381-399).
   float top = -INFINITY;
-  for (int i = 0; i < splits; ++i) top = fmaxf(top, lse_partial[((int64_t)i * heads + head) * rows + row]);
+  int top_share = 0;
+  for (int i = 0; i < splits; ++i) {
+    const float value = lse_partial[((int64_t)i * heads + head) * rows + row];
+    if (value > top) {
+      top = value;
+      top_share = i;
+    }
+  }
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  float total = 0.f;
+  float rest = 0.f;
   if (top != -INFINITY) {
     for (int i = 0; i < splits; ++i) {
-      const float w = __expf(lse_partial[((int64_t)i * heads + head) * rows + row] - top);
+      const float w = i == top_share ? 1.f : __expf(lse_partial[((int64_t)i * heads + head) * rows + row] - top);
       const float4 o = *reinterpret_cast<const float4*>(o_partial + (((int64_t)i * rows + row) * heads + head) * head_dim + 4 * g);
       acc.x += w * o.x;
       acc.y += w * o.y;
       acc.z += w * o.z;
       acc.w += w * o.w;
-      total += w;
+      if (i != top_share) rest += w;
     }
   }
+  const float total = top != -INFINITY ? 1.f + rest : 0.f;
   const float inv = total > 0.f ? 1.f / total : 0.f;
   const int64_t b = row / seqlen_q, r = row - b * seqlen_q;
   uint2 packed;
   packed.x = pack_bf16x2(acc.x * inv, acc.y * inv);
   packed.y = pack_bf16x2(acc.z * inv, acc.w * inv);
   *reinterpret_cast<uint2*>(out + b * o_bs + r * o_rs + (int64_t)head * o_hs + 4 * g) = packed;
-  if (g == 0) lse[b * lse_bs + (int64_t)head * lse_hs + r] = total > 0.f ? top + logf(total) : -INFINITY;
+  if (g == 0) lse[b * lse_bs + (int64_t)head * lse_hs + r] = total > 0.f ? top + log1pf(rest) : -INFINITY;
 }
 
 int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim, int tile_rows, int kv_box_rows,

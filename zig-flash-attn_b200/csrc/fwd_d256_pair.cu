@@ -318,6 +318,7 @@ fwd_d256_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kPairRows, t.s.lq));
       const int band_lo = cur.band.lo(row), band_hi = cur.band.hi(row);
       float m = -INFINITY, l = 0.f;
+      TopApart top;  // keys set aside for the log-sum-exp of rows with a near-zero maximum (fwd_common.cuh)
       int tile_blocks = 0;
       OtherBlock kb;
       while (cur.next(&kb)) {
@@ -371,7 +372,11 @@ fwd_d256_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         tmem_ld32(t_s + 96, reinterpret_cast<uint32_t*>(high) + 32);
         tc_wait_ld();
         if (masked) apply_mask(high, 64);
-        const float m_new = fmaxf(m, fmaxf(max_low, max_of(high)));
+        const float max_high = max_of(high);
+        const float block_max = fmaxf(max_low, max_high);
+        const float m_new = fmaxf(m, block_max);
+        const bool set_apart = sets_keys_apart(top, max_low, max_high, scale_log2);
+        const bool counting = __any_sync(0xffffffffu, set_apart);
         trace_event(wctx, traced, trole, trace_n, 6000 + 1000 * (int)rank + (tile_blocks % 100));  // row maximum known
         const bool grow = (m_new - m) * scale_log2 > 8.f;  // also true when m is -inf and m_new is finite
         if (__any_sync(0xffffffffu, grow)) {
@@ -398,6 +403,9 @@ fwd_d256_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
         const float mc = (m == -INFINITY) ? 0.f : m * scale_log2;
         const float2 scale2 = make_float2(scale_log2, scale_log2), shift2 = make_float2(-mc, -mc);
+        float sum_counted = 0.f;
+        if (counting)  // rare: the block sum without the keys set aside, from the scores still in TMEM
+          sum_counted = sum_without_keys_apart<kBlockN>(top, l, set_apart, block_max, t_s, masked, lo, hi, scale_log2, mc);
         float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
         // 64 scores -> 64 probabilities (BF16) stored at P columns [first_p_column, first_p_column + 32)
         auto exponentiate = [&](const float2* values, uint32_t first_p_column) {
@@ -429,7 +437,7 @@ fwd_d256_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         tc_wait_ld();
         if (masked) apply_mask(low, 0);
         exponentiate(low, 0);
-        l += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
+        l += counting ? sum_counted : (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
         // Observe the PV product of the previous block before releasing this one: the scores of block n only prove that
         // PV(n - 2) has completed, and a parity wait cannot tell a barrier that is two completions behind from one that
         // is done.
@@ -459,7 +467,9 @@ fwd_d256_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       }
       if (!mbar_wait_warp(bar_pv_done, (blocks - 1) & 1, wctx, kWaitEpilogue)) { ok = false; break; }
       tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      float total, lse_row;
+      row_totals(m, l, top.ones, top.apart, top.row_max, scale_log2, &total, &lse_row);
+      const float inv = total > 0.f ? 1.f / total : 0.f;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
@@ -477,10 +487,7 @@ fwd_d256_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           }
         }
       }
-      if (row_valid) {
-        const float mc = (m == -INFINITY) ? 0.f : m * scale_log2;
-        *lse_ptr = l > 0.f ? (mc + log2f(l)) * 0.69314718055994531f : -INFINITY;
-      }
+      if (row_valid) *lse_ptr = lse_row;
       tc_fence_before();
     }
   }

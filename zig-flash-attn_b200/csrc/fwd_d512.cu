@@ -257,6 +257,7 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kBlockM, t.s.lq));
       const int band_lo = cur.cursor.band.lo(row), band_hi = cur.cursor.band.hi(row);
       float m = -INFINITY, l = 0.f;
+      TopApart top;  // keys set aside for the log-sum-exp of rows with a near-zero maximum (fwd_common.cuh)
       int tile_blocks = 0;
       OtherBlock kb;
       while (cur.next(&kb)) {
@@ -277,7 +278,8 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           lo = 0;
           hi = kb.limit - kb.col0;
         }
-        if (__any_sync(0xffffffffu, lo > 0 || hi < kSubN)) {
+        const bool masked_block = __any_sync(0xffffffffu, lo > 0 || hi < kSubN);
+        if (masked_block) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             s[i].x = (2 * i >= lo && 2 * i < hi) ? s[i].x : -INFINITY;
@@ -293,7 +295,11 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           bm2 = fmaxf(bm2, fmaxf(s[i + 2].x, s[i + 2].y));
           bm3 = fmaxf(bm3, fmaxf(s[i + 3].x, s[i + 3].y));
         }
-        const float m_new = fmaxf(m, fmaxf(fmaxf(bm0, bm1), fmaxf(bm2, bm3)));
+        const float part_a = fmaxf(bm0, bm1), part_b = fmaxf(bm2, bm3);  // two disjoint parts of the block
+        const float block_max = fmaxf(part_a, part_b);
+        const float m_new = fmaxf(m, block_max);
+        const bool set_apart = sets_keys_apart(top, part_a, part_b, scale_log2);
+        const bool counting = __any_sync(0xffffffffu, set_apart);
         const bool grow = (m_new - m) * scale_log2 > 8.f;  // also true when m is -inf and m_new is finite
         if (__any_sync(0xffffffffu, grow)) {
           float alpha = 1.f;
@@ -319,6 +325,9 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         const float mc = (m == -INFINITY) ? 0.f : m * scale_log2;
         const float2 scale2 = make_float2(scale_log2, scale_log2), shift2 = make_float2(-mc, -mc);
+        float sum_counted = 0.f;
+        if (counting)  // rare: the block sum without the keys set aside, from the scores still in TMEM
+          sum_counted = sum_without_keys_apart<kSubN>(top, l, set_apart, block_max, t_s, masked_block, lo, hi, scale_log2, mc);
         float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -334,7 +343,7 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
           tmem_st16(t_s + 64 + 16 * c, packed);
         }
-        l += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
+        l += counting ? sum_counted : (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
         // Observe the PV product of the previous block before releasing this one. The scores of block n only prove
         // that PV(n - 2) has completed, so without this wait the barrier could be two completions away from the one
         // the epilogue waits for, which a parity wait cannot tell apart from "done".
@@ -362,7 +371,9 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
       if (!mbar_wait_warp(bar_pv_done, (blocks - 1) & 1, wctx, kWaitEpilogue)) { ok = false; break; }
       tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      float total, lse_row;
+      row_totals(m, l, top.ones, top.apart, top.row_max, scale_log2, &total, &lse_row);
+      const float inv = total > 0.f ? 1.f / total : 0.f;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
@@ -380,10 +391,7 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
         }
       }
-      if (row_valid && dh == 0) {  // both halves hold the same statistics
-        const float mc = (m == -INFINITY) ? 0.f : m * scale_log2;
-        *lse_ptr = l > 0.f ? (mc + log2f(l)) * 0.69314718055994531f : -INFINITY;
-      }
+      if (row_valid && dh == 0) *lse_ptr = lse_row;  // both halves hold the same statistics
       tc_fence_before();
     }
   }

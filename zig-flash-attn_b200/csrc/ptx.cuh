@@ -326,6 +326,10 @@ __device__ __forceinline__ float ld_shared_f32(uint32_t addr) {
 }
 
 // ---------------------------------------------------------------- small math helpers
+__device__ __forceinline__ void red_add_f32(float* address, float value) {
+  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(address), "f"(value) : "memory");
+}
+
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

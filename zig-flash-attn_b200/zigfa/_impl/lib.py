@@ -23,6 +23,7 @@ EXPORTS = (
     "b200fa_bwd_workspace_bytes",
     "b200fa_bwd",
     "b200fa_bwd_timing_events",
+    "b200fa_set_pivot_ds",
     "b200fa_set_trace",
     "b200fa_interseq_metadata",
     "b200fa_work_list",
@@ -132,6 +133,8 @@ def library() -> ctypes.CDLL:
     lib.b200fa_bwd.argtypes = [ctypes.POINTER(BwdArgs), ctypes.c_void_p]
     lib.b200fa_bwd_timing_events.restype = ctypes.c_int
     lib.b200fa_bwd_timing_events.argtypes = [ctypes.POINTER(ctypes.c_void_p)]
+    lib.b200fa_set_pivot_ds.restype = ctypes.c_int
+    lib.b200fa_set_pivot_ds.argtypes = [ctypes.c_int]
     lib.b200fa_set_trace.restype = ctypes.c_int
     lib.b200fa_set_trace.argtypes = [ctypes.c_void_p]
     lib.b200fa_interseq_metadata.restype = ctypes.c_int
