@@ -122,7 +122,7 @@ int b200fa_bwd(const b200fa_bwd_args* args, void* stream);
  * The setting is process-wide, read at every b200fa_bwd call; it starts as 1 when the environment variable
  * B200FA_PIVOT_DS is "1" and as 0 otherwise (the pivot path costs the backward main kernel about 16 %; without it the
  * gradients stay within the stated tolerance of the BF16 reference). Returns the previous value; a negative `enabled`
- * only queries. The head_dim 256 kernel has no pivot path. */
+ * only queries. */
 int b200fa_set_pivot_ds(int enabled);
 
 /* Measurement hook (no counterpart in the reference): the next b200fa_bwd call of the calling thread records the four

@@ -40,7 +40,7 @@ KEY_SHIFT = 96.0
 OTHER_SCALE = 0.2
 GQA_HEADS = (4, 2)
 WINDOWS = {"dense": (-1, -1), "causal": (-1, 0), "local": (64, 32)}
-HEAD_DIMS = (64, 128)
+HEAD_DIMS = (64, 128, 256)
 
 
 class Problem:

@@ -835,11 +835,11 @@ static BwdWorkspace plan_workspace(const b200fa_problem& p) {
   w.dq_accum = 4 * stat_bytes;
   const int compiled_dim = p.head_dim <= 64 ? 64 : p.head_dim <= 128 ? 128 : 256;  // the accumulator has the compiled width
   const size_t acc_bytes = ((size_t)p.heads_q * w.rows * compiled_dim * 4 + 255) & ~size_t(255);
-  // Pivot terms of dK (head_dim <= 128): 256 bytes that hold the "some row has a pivot" flag, then
-  // (heads_kv, key rows, compiled width) FP32; one memset zeroes both.
+  // Pivot terms of dK: 256 bytes that hold the "some row has a pivot" flag, then (heads_kv, key rows, compiled width)
+  // FP32; one memset zeroes both.
   w.key_rows = packed ? (int64_t)p.seqlen_k : (int64_t)p.batch * p.seqlen_k;
   w.dk_fix = w.dq_accum + acc_bytes;
-  w.dk_fix_bytes = compiled_dim <= 128 ? 256 + (((size_t)p.heads_kv * w.key_rows * compiled_dim * 4 + 255) & ~size_t(255)) : 0;
+  w.dk_fix_bytes = 256 + (((size_t)p.heads_kv * w.key_rows * compiled_dim * 4 + 255) & ~size_t(255));
   w.work_list = w.dk_fix + w.dk_fix_bytes;
   w.entries = packed ? work_list_entries(p.seqlen_k, p.batch, kBlockN) : 0;
   w.total = w.work_list + (size_t)w.entries * 8;
@@ -919,7 +919,7 @@ static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
   float* dq_accum = reinterpret_cast<float*>(ws + w.dq_accum);
   float* pivot_sum = reinterpret_cast<float*>(ws + w.pivot_sum);
   int* pivot_key = reinterpret_cast<int*>(ws + w.pivot_key);
-  // Pivot gradients: on request (b200fa_set_pivot_ds); the head_dim 256 kernel has no pivot handling.
+  // Pivot gradients: on request (b200fa_set_pivot_ds).
   const bool pivots = pivot_ds_enabled() && w.dk_fix_bytes > 0 && w.rows > 0 && w.key_rows > 0;
   int* any_pivot = reinterpret_cast<int*>(ws + w.dk_fix);
   float* dk_fix = reinterpret_cast<float*>(ws + w.dk_fix + 256);

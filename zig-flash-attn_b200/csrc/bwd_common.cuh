@@ -26,7 +26,7 @@ struct BwdParams {
   // Pivot rows (at most one key of a query row holds more than 3/4 of its probability): the main kernel leaves the dS
   // of that key out, records the key in `pivot_key` (tensor row of K, -1 = none) and adds the BF16 dS of the other keys,
   // times kPivotSumScale, into `pivot_sum`; the postprocess kernel takes the dS of the pivot as minus that sum. Both are
-  // (heads_q, rows). Null: the kernel has no pivot handling (head_dim 256).
+  // (heads_q, rows). Null: pivot gradients are off (b200fa_set_pivot_ds).
   float* pivot_sum;
   int* pivot_key;
   int head_dim;           // columns of the tensors (<= the compiled D; TMA zero-fills the columns in between)

@@ -83,6 +83,7 @@ struct HalfBlockCursor {
   }
 };
 
+template <bool kPivot>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
@@ -126,7 +127,7 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t bar_final = bars + 64, bar_v_ready = bars + 72;
   const uint32_t bar_q_full = bars + 80 /*[2]*/, bar_q_empty = bars + 96 /*[2]*/, bar_do_full = bars + 112 /*[2]*/;
   const uint32_t bar_do_empty = bars + 128 /*[2]*/;
-  const uint32_t tmem_slot = bars + 144, abort_slot = bars + 148;
+  const uint32_t tmem_slot = bars + 144, abort_slot = bars + 148, bar_ds_free = bars + 152;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + (abort_slot - base));
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - base));
   const WaitCtx wctx{abort_flag, p.status, nullptr};
@@ -151,6 +152,7 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     mbar_init(bar_dq_full, 1);
     mbar_init(bar_dq_empty, 128 * kDrains);
     mbar_init(bar_final, 1);
+    mbar_init(bar_ds_free, 128 * kDrains);
     fence_barrier_init();
   }
   if (warp == kMmaWarp) {
@@ -401,11 +403,31 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar_p_full);
+        // A probability above 3/4 is the pivot of its query row (see bwd.cu): dV keeps it, dS leaves it out. Both CTAs
+        // of a key block (the two halves of the head dimension) compute the same scores; the first one records the key.
+        if constexpr (kPivot) {
+          float2 total = make_float2(pf[0], pf[1]);
+#pragma unroll
+          for (int j = 2; j < kCols; j += 2) total = __fadd2_rn(total, make_float2(pf[j], pf[j + 1]));
+          if (__any_sync(0xffffffffu, total.x + total.y > kPivotProbability)) {
+            const int head = kv_head * group + g;
+            int* keys = p.pivot_key + (int64_t)head * p.rows + stat_base + qb.row + cb;
+#pragma unroll
+            for (int j = 0; j < kCols; ++j) {
+              if (pf[j] > kPivotProbability) {
+                if (dh == 0) keys[j] = s.k0 + c;
+                pf[j] = 0.f;
+              }
+            }
+          }
+        }
         // ---- dS^T = P^T o (dP^T - D), written to shared memory as BF16
         if (!mbar_wait(bar_dp_full, it & 1, wctx, kWaitBwdCompute)) { ok = false; break; }
         // The dS tile of the previous iteration must have been consumed by its dK and dQ MMAs.
         // (announced by the commit that releases the Q stage of that iteration, issued after the same MMAs)
         if (it > 0 && !mbar_wait(bar_q_empty + 8 * ((it - 1) & 1), ((it - 1) >> 1) & 1, wctx, kWaitBwdCompute)) { ok = false; break; }
+        // ... and summed over its keys by the drain warps (pivot rows).
+        if (kPivot && it > 0 && !mbar_wait(bar_ds_free, (it - 1) & 1, wctx, kWaitBwdCompute)) { ok = false; break; }
         tc_fence_after();
         float dp[kCols];
         tmem_ld16(t_dp + cb, reinterpret_cast<uint32_t*>(dp));
@@ -527,6 +549,51 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             bulk_commit_group();
           }
         }
+        // Sums of the BF16 dS over the 128 keys of the block for the 64 queries of the iteration, as in bwd.cu: the first
+        // four drain warps take two 16-byte chunks (8 queries) each, lane = (key row mod 16, chunk). Only the CTA of the
+        // first half of the head dimension adds them to pivot_sum (the other half holds the same scores).
+        if constexpr (kPivot) {
+          if (!mbar_wait(bar_ds_full, it & 1, wctx, kWaitBwdReduce)) { ok = false; break; }
+          const int drain_warp = warp - kComputeWarps;
+          float sum = 0.f;
+          const int sel = lane & 1, row_lane = lane >> 1;
+          const int chunk = 2 * (drain_warp & 3) + sel;  // queries [8 chunk, 8 chunk + 8)
+          if (drain_warp < 4 && dh == 0) {
+            float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int key = 16 * i + row_lane;
+              const float4 w = ld_shared_f4(smem_ds + key * 128 + ((chunk ^ (key & 7)) << 4));
+              const uint32_t words[4] = {__float_as_uint(w.x), __float_as_uint(w.y), __float_as_uint(w.z), __float_as_uint(w.w)};
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                acc[j] = __fadd2_rn(acc[j], make_float2(__uint_as_float(words[j] << 16), __uint_as_float(words[j] & 0xffff0000u)));
+            }
+            float v[8] = {acc[0].x, acc[0].y, acc[1].x, acc[1].y, acc[2].x, acc[2].y, acc[3].x, acc[3].y};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const bool upper = lane & 16;
+              const float send = upper ? v[k] : v[k + 4], keep = upper ? v[k + 4] : v[k];
+              v[k] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+            }
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+              const bool upper = lane & 8;
+              const float send = upper ? v[k] : v[k + 2], keep = upper ? v[k + 2] : v[k];
+              v[k] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+            }
+            {
+              const bool upper = lane & 4;
+              const float send = upper ? v[0] : v[1], keep = upper ? v[1] : v[0];
+              v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+            }
+            sum = v[0] + __shfl_xor_sync(0xffffffffu, v[0], 2);
+          }
+          mbar_arrive(bar_ds_free);  // before the reductions: the arrive has release semantics
+          const int64_t row = stat_base + qb.row + 8 * chunk + ((lane >> 2) & 7);
+          if (drain_warp < 4 && dh == 0 && (lane & 2) == 0 && sum != 0.f && row < p.rows)
+            red_add_f32(p.pivot_sum + (int64_t)head * p.rows + row, sum * kPivotSumScale);
+        }
         ++it;
       }
     }
@@ -583,10 +650,17 @@ int launch_bwd_main_d256(const b200fa_bwd_args& a, const BwdParams& p, dim3 grid
                                stat_rows * D, D, (int64_t)bp.heads_q * stat_rows * D, 128, kStageRows);
     if (status != B200FA_OK) return status;
   }
-  static bool attribute_set[64] = {false};
-  status = set_dynamic_smem_once(reinterpret_cast<const void*>(&bwd_d256_kernel), kSmemBytes, attribute_set);
-  if (status != B200FA_OK) return status;
-  bwd_d256_kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, map_do, map_dq, p);
+  if (p.pivot_key) {  // pivot gradients requested (b200fa_set_pivot_ds)
+    static bool attribute_set[64] = {false};
+    status = set_dynamic_smem_once(reinterpret_cast<const void*>(&bwd_d256_kernel<true>), kSmemBytes, attribute_set);
+    if (status != B200FA_OK) return status;
+    bwd_d256_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, map_do, map_dq, p);
+  } else {
+    static bool attribute_set[64] = {false};
+    status = set_dynamic_smem_once(reinterpret_cast<const void*>(&bwd_d256_kernel<false>), kSmemBytes, attribute_set);
+    if (status != B200FA_OK) return status;
+    bwd_d256_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, map_do, map_dq, p);
+  }
   B200FA_CUDA_CHECK(cudaGetLastError());
   return B200FA_OK;
 }
