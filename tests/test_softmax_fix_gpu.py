@@ -425,3 +425,118 @@ def test_random_rows_keep_their_accuracy(head_dim, query_scale):
         if name == "dk":
             allowed = allowed + 0.5 * bf16_spacing(exact)[ref["corrected_keys"]].norm()
         assert float((gradient.double() - exact).norm()) <= float(allowed), name
+
+
+# ------------------------------------------------------------------------------------------------ inter-sequence batches
+def inter_sequence_problem(layout, heads, heads_kv, head_dim):
+    cu_q, cu_k, bits, window_sizes = layout.tensors()
+    arguments = (cu_q, cu_k, max(layout.lengths_q), max(layout.lengths_k), bits)
+
+    def attend(q, k, v):
+        return zigfa.flash_attn_inter_sequence_func(q, k, v, *arguments, window_sizes=window_sizes, return_attn_probs=True)
+
+    mask = oracle.inter_sequence_mask(cu_q.tolist(), cu_k.tolist(), layout.visible, layout.windows).cuda()
+    tensors = random_tensors(sum(layout.lengths_q), sum(layout.lengths_k), heads, heads_kv, head_dim)
+    return tensors, mask, attend, cu_k.long()
+
+
+@pytest.mark.parametrize("head_dim", (64, 128, 256, 512))
+@pytest.mark.parametrize("layout_name", ["image_then_text", "shared_prefix", "interleaved"])
+def test_zero_maximum_and_peaked_inter_sequence_rows(head_dim, layout_name):
+    """Visibility-bit batches (reference tests/test_softmax_fix.py:552-572): the first key of every sequence scores zero;
+    then attention sinks and random peaks. head_dim 512 has a forward kernel only."""
+    from test_inter_sequence_gpu import build_layout
+
+    layout = build_layout(layout_name, 4)
+    (heads, heads_kv), gradients = GQA_HEADS, head_dim <= 256
+    torch.manual_seed(head_dim)
+    (q, k, v, dout), mask, attend, cu_k = inter_sequence_problem(layout, heads, heads_kv, head_dim)
+    zero_keys = torch.zeros(k.shape[:2], dtype=torch.bool, device="cuda")
+    zero_keys[cu_k[:-1][torch.tensor(layout.lengths_k, device="cuda") > 0]] = True
+    zq, zk = with_zero_maximum(q, k, mask, zero_keys, head_dim**-0.5)
+    check(Problem(zq, zk, v, dout, mask, attend), gradients, zero_maximum=True, pivots_required=gradients)
+    if gradients:
+        for choice in (first_visible_keys, random_visible_keys):
+            peaked_q = with_peaks(q, k, mask, choice(mask, heads), head_dim**-0.5)
+            check(Problem(peaked_q, k, v, dout, mask, attend), pivots_required=True)
+
+
+# ------------------------------------------------------------------------------------------------ ties at a large shift
+# Scores on a grid of 1/8 at a common shift of 2^16 or 2^17, built exactly in BF16 from one-hot queries (reference
+# tests/test_softmax_fix.py:742-781,798-815): the FP32 product of such a score and log2(e) rounds by up to 2^-8 or 2^-7, and
+# the log-sum-exp must carry that remainder instead of counting a tied key as an exact 1.
+TIE_SHIFTS = (2.0**16, 2.0**17)
+TIE_SCORES = torch.arange(-64, -7, dtype=torch.float64) / 8
+FAR_SCORE = 1000.0
+LOG2_SUM_SLACK = 2.0**-17
+FAR_ROUNDING = 0.375
+
+
+def float32(x):
+    return float(torch.tensor(x, dtype=torch.float32))
+
+
+def fp32_spacing(x):
+    _, exponent = torch.frexp(x)
+    return torch.ldexp(torch.ones_like(x), exponent - 24)
+
+
+def lse_of_scores(scores, shift, head_dim):
+    """Runs a dense forward whose scores are exactly `shift + scores` (heads, rows, keys) with softmax_scale 1."""
+    heads, rows, keys = scores.shape
+    q = torch.zeros(rows, heads, head_dim, dtype=torch.float64)
+    q[torch.arange(rows), :, torch.arange(rows)] = 1.0
+    q[..., -1] = 1.0
+    k = torch.zeros(keys, heads, head_dim, dtype=torch.float64)
+    k[..., :rows] = scores.permute(2, 0, 1)
+    k[..., -1] = shift
+    v = torch.randn(keys, heads, head_dim, generator=torch.Generator().manual_seed(head_dim), dtype=torch.float64)
+    attend = fixed_attention(1, WINDOWS["dense"], 1.0)
+    return attend(*(x.cuda().bfloat16() for x in (q, k, v)))[1].double()
+
+
+def base2_log_sum_exp(scores, shift):
+    x = (shift + scores.cuda()) * float32(math.log2(math.e))
+    top = x.amax(-1, keepdim=True)
+    return (top + (x - top).exp2().sum(-1, keepdim=True).log2())[..., 0]
+
+
+def check_log2_sum(name, lse, log2_sum, exp2_error=0.0):
+    ln2 = float32(math.log(2))
+    allowed = ln2 * (fp32_spacing(log2_sum) / 2 + LOG2_SUM_SLACK) + fp32_spacing(lse) / 2 + exp2_error
+    worst(name, (lse - log2_sum * ln2).abs() / allowed, torch.ones_like(lse, dtype=torch.bool))
+
+
+@pytest.mark.parametrize("head_dim", HEAD_DIMS)
+def test_rows_tied_at_a_large_shift_keep_their_lse_within_fp32_rounding(head_dim):
+    heads, rows, keys, positions = 4, 16, 320, (66, 67, 70, 200)
+    ties = TIE_SCORES[torch.arange(heads * rows) % len(TIE_SCORES)].reshape(heads, rows, 1)
+    where = torch.tensor(positions).expand(heads, rows, -1)
+    scores = torch.full((heads, rows, keys), -FAR_SCORE, dtype=torch.float64).scatter(2, where, ties.expand_as(where))
+    for shift in TIE_SHIFTS:
+        check_log2_sum("lse of rows tied at the maximum", lse_of_scores(scores, shift, head_dim), base2_log_sum_exp(scores, shift))
+
+
+@pytest.mark.parametrize("head_dim", HEAD_DIMS)
+def test_diffuse_rows_at_a_large_shift_keep_their_lse_within_fp32_rounding(head_dim):
+    """One top key, eight keys up to 2 nats below in the same group of 16, two keys 6 and 6.5 nats below elsewhere
+    (reference tests/test_softmax_fix.py:947-976)."""
+    heads, rows, keys = 4, 32, 320
+    near, far, groups, top_offset = (3, 5, 6, 9, 10, 12, 13, 15), {10: 6.0, 300: 6.5}, (64, 192), 2
+    generator = torch.Generator().manual_seed(head_dim)
+    log2_e = torch.tensor(math.log2(math.e), dtype=torch.float32).double()
+    for shift in TIE_SHIFTS:
+        exact = (shift + TIE_SCORES) * log2_e
+        _, exponent = torch.frexp(exact.float().double())
+        units = (exact - exact.float().double()).abs() / torch.ldexp(torch.ones_like(exact), exponent - 24)
+        candidates = TIE_SCORES[units >= FAR_ROUNDING]  # scores whose product with log2(e) rounds far in FP32
+        tops = candidates[torch.randint(len(candidates), (heads, rows, 1), generator=generator)]
+        gaps = torch.randint(1, 17, (heads, rows, len(near)), generator=generator) / 8
+        scores = torch.full((heads, rows, keys), -FAR_SCORE, dtype=torch.float64)
+        for head in range(heads):
+            group = groups[head % len(groups)]
+            scores[head, :, group + top_offset] = tops[head, :, 0]
+            scores[head, :, [group + offset for offset in near]] = tops[head] - gaps[head]
+        for position, gap in far.items():
+            scores[..., position] = tops[..., 0] - gap
+        check_log2_sum("lse of diffuse rows", lse_of_scores(scores, shift, head_dim), base2_log_sum_exp(scores, shift), EXP2_ERROR)
