@@ -393,6 +393,22 @@ def other_workloads(device, peaks):
         records[name] = rates(flops_fwd, budgeted_time(forward), budgeted_time(backward), peaks, batch * seqlen)
         del forward, backward
         torch.cuda.empty_cache()
+    # Config 1 with the pivot path of the backward on (zigfa.set_pivot_gradients): what the reference's stricter accuracy
+    # guarantees for peaked rows cost; the headline runs with the default, off.
+    import zigfa
+
+    batch, seqlen, heads_q, heads_kv, d, window = 4, 8192, 32, 8, 128, (-1, 0)
+    forward, backward, flops_fwd = fixed_problem(batch, seqlen, heads_q, heads_kv, d, window, 17, device)
+    forward()
+    before = zigfa.set_pivot_gradients(True)
+    try:
+        backward()
+        records["c1_backward_with_pivot_gradients"] = rates(flops_fwd, budgeted_time(forward), budgeted_time(backward), peaks,
+                                                            batch * seqlen)
+    finally:
+        zigfa.set_pivot_gradients(before)
+    del forward, backward
+    torch.cuda.empty_cache()
     for name, key, d, with_backward in (("c2_packed_window", "c2", None, True), ("c3_inter_sequence_d256", "c3", None, True),
                                         ("c3_inter_sequence_d512_forward", "c3", 512, False)):
         forward, backward, flops_fwd, total, sequences = packed_problem(WORKLOADS[key], device, d)

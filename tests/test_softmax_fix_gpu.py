@@ -540,3 +540,166 @@ def test_diffuse_rows_at_a_large_shift_keep_their_lse_within_fp32_rounding(head_
         for position, gap in far.items():
             scores[..., position] = tops[..., 0] - gap
         check_log2_sum("lse of diffuse rows", lse_of_scores(scores, shift, head_dim), base2_log_sum_exp(scores, shift), EXP2_ERROR)
+
+
+# ------------------------------------------------------------------------------------------------ subnormal sums
+# Two keys with the score -(83 + 7/64) and dP of 1 and -(1 - 2^-7) get BF16 dS whose sum is 2^-127, an FP32 subnormal
+# number; a key with the score -(76 + 21/128) carries most of the remaining weight of its row (reference
+# tests/test_softmax_fix.py:54-62,640-661).
+PAIR_SCORE, PAIR_VALUE, HEAVY_SCORE = (83.0, 7 / 64), -(1 - 2.0**-7), (76.0, 21 / 128)
+ORTHOGONAL_SHIFT, ROW_SUM_UNIT = 2.0**40, 2.0**-20
+
+
+def subnormal_pair_problem(head_dim, shift, q=None, dout=None, seqlen_q=16):
+    batch, seqlen_k = 2, 130
+    layouts = ({1: (PAIR_SCORE, 1.0), 2: (PAIR_SCORE, PAIR_VALUE)},
+               {1: (HEAVY_SCORE, 1.0), 128: (PAIR_SCORE, 1.0), 129: (PAIR_SCORE, PAIR_VALUE)})
+    if q is None:
+        q = torch.zeros(batch * seqlen_q, 1, head_dim, device="cuda", dtype=torch.float64)
+        q[..., :2] = 1.0
+    k = torch.zeros(batch * seqlen_k, 1, head_dim, device="cuda", dtype=torch.float64)
+    v = torch.zeros_like(k)
+    k[..., 0] = -FAR_SCORE
+    for sequence, keys in enumerate(layouts):
+        first = sequence * seqlen_k
+        k[first, :, 0] = 0.0
+        for key, ((whole, fraction), value) in keys.items():
+            k[first + key, :, 0], k[first + key, :, 1], v[first + key, :, 0] = -whole, -fraction, value
+    k[..., 2] = shift
+    if dout is None:
+        dout = torch.zeros_like(q)
+        dout[..., 0] = 1.0
+    window = WINDOWS["dense"]
+    mask = fixed_mask(batch, q.shape[0] // batch, seqlen_k, window)
+    return Problem(q, k, v, dout, mask, fixed_attention(batch, window, 1.0), 1.0)
+
+
+def exact_ds(problem):
+    q, k, v, dout = (x.double()[:, 0] for x in (problem.q, problem.k, problem.v, problem.dout))
+    p = (problem.softmax_scale * q @ k.T).masked_fill(~problem.mask, float("-inf")).softmax(-1)
+    dp = dout @ v.T
+    return p * (dp - (p * dp).sum(-1, keepdim=True))
+
+
+@pytest.mark.parametrize("head_dim", HEAD_DIMS)
+def test_query_gradient_ignores_a_key_shift_on_rows_with_subnormal_ds_sums(head_dim):
+    """A shift of 2^40 along an axis that every query ignores multiplies the sum of the dS of a row: the sum of the BF16
+    dS of the others, an FP32 subnormal number here, must reach the pivot unflushed (reference
+    tests/test_softmax_fix.py:671-690)."""
+    problem, shifted = subnormal_pair_problem(head_dim, 0.0), subnormal_pair_problem(head_dim, ORTHOGONAL_SHIFT)
+    assert (shifted.k[..., 2] == ORTHOGONAL_SHIFT).all(), "the shifted keys are exact in bfloat16"
+    ds = exact_ds(problem)
+    pair = ds[0, 1:3].bfloat16().double().sum().abs()
+    assert 0 < pair < 2.0**-126, "the BF16 dS of the key pair sum to an FP32 subnormal number"
+    _, _, dq, _, _ = problem.run()
+    _, _, shifted_dq, _, _ = shifted.run()
+    allowed = ROW_SUM_UNIT * ORTHOGONAL_SHIFT * problem.softmax_scale * ds.abs().sum(-1, keepdim=True)
+    ratio = (shifted_dq.double() - dq.double()).norm(dim=-1) / allowed
+    worst("dq change under a key shift orthogonal to the queries", ratio, torch.ones_like(ratio, dtype=torch.bool))
+
+
+@pytest.mark.parametrize("head_dim", HEAD_DIMS)
+def test_pivot_key_gradient_keeps_subnormal_sums_of_terms(head_dim):
+    """Every row of the first sequence gives its pivot key the BF16 dS -2^-127; query columns that every key ignores give
+    that key dK terms of -2^-133 and -2^-137 per row, which sum to FP32 subnormal numbers over the 16 rows (reference
+    tests/test_softmax_fix.py:693-706)."""
+    columns = {3: 2.0**-6, 4: 2.0**-10}
+    pair = subnormal_pair_problem(head_dim, 0.0)
+    q = pair.q.double().clone()
+    q[..., list(columns)] = q.new_tensor(list(columns.values()))
+    problem = subnormal_pair_problem(head_dim, 0.0, q=q)
+    rows = slice(0, q.shape[0] // 2)
+    row_sums = exact_ds(problem)[rows, 1:].bfloat16().double().sum(-1)
+    expected = -problem.softmax_scale * (row_sums @ problem.q[rows, 0, list(columns)].double())
+    assert (expected.abs() < 2.0**-126).all() and (expected != 0).all(), "the dK terms of the pivot key sum to subnormal numbers"
+    _, _, _, dk, _ = problem.run()
+    assert (dk[0, 0, list(columns)].double() == expected.bfloat16().double()).all(), (dk[0, 0, list(columns)], expected)
+
+
+@pytest.mark.parametrize("head_dim", HEAD_DIMS)
+def test_pivot_key_gradient_mixes_subnormal_and_large_sums_in_one_word(head_dim):
+    """512 rows whose dS sum is 2^-127: one query column gives the pivot key terms of -2^-133 (first half of the rows)
+    and -2^-27 (second half) in the same word, another only terms of -2^-137 (reference
+    tests/test_softmax_fix.py:1020-1045)."""
+    mixed_column, small, large, small_only_column, small_only, seqlen_q = 3, 2.0**-6, 2.0**100, 4, 2.0**-10, 512
+    pair = subnormal_pair_problem(head_dim, 0.0)
+    q = pair.q[:1].double().expand(2 * seqlen_q, -1, -1).clone()
+    half = seqlen_q // 2
+    for sequence in range(2):
+        first = sequence * seqlen_q
+        q[first : first + half, :, mixed_column] = small
+        q[first + half : first + seqlen_q, :, mixed_column] = large
+        q[first : first + seqlen_q, :, small_only_column] = small_only
+    dout = pair.dout[:1].double().expand(2 * seqlen_q, -1, -1).clone()
+    problem = subnormal_pair_problem(head_dim, 0.0, q=q, dout=dout)
+    rows, columns = slice(0, seqlen_q), [mixed_column, small_only_column]
+    row_sums = exact_ds(problem)[rows, 1:].bfloat16().double().sum(-1)
+    assert (row_sums == 2.0**-127).all(), "every row of the first sequence has the dS sum 2^-127"
+    expected = -problem.softmax_scale * (row_sums @ problem.q[rows, 0, columns].double())
+    assert expected[0] == -half * 2.0**-27 and expected[1].abs() < 2.0**-126
+    _, _, _, dk, _ = problem.run()
+    assert (dk[0, 0, columns].double() == expected.bfloat16().double()).all(), (dk[0, 0, columns], expected)
+
+
+# ------------------------------------------------------------------------------------------------ ties across key splits
+def test_keys_tied_across_key_splits_at_a_large_shift_keep_the_unsplit_output():
+    """Four keys tie at the row maximum, each in another share of a split-KV forward; the output must stay within 0.05
+    BF16 units (mean) of the unsplit run, and so must a run with the ties gathered in one key block (reference
+    tests/test_softmax_fix.py:829-861). The unsplit run is b200fa_fwd without a workspace."""
+    import ctypes
+
+    from zigfa._impl import lib
+
+    head_dim, rows, keys, heads, tied = 128, 16, 4096, 2, 4
+    spread = torch.arange(tied) * (keys // tied) + 5
+    gathered = torch.tensor((2, 3, 6, 13))
+    order = torch.arange(keys)
+    order[spread], order[gathered] = gathered, spread
+    generator = torch.Generator().manual_seed(head_dim)
+    log2_e = torch.tensor(math.log2(math.e), dtype=torch.float32).double()
+    library, stream = lib.library(), torch.cuda.current_stream().cuda_stream
+
+    def forward(q, k, v, split):
+        q, k, v = (x[None].contiguous() for x in (q, k, v))
+        out = torch.full_like(q, float("nan"))
+        lse = torch.full((1, heads, rows), float("nan"), device="cuda")
+        problem = lib.make_problem(q, k, None, None, 1.0, -1, -1)
+        nbytes = library.b200fa_fwd_workspace_bytes(ctypes.byref(problem)) if split else 0
+        assert not split or nbytes > 0, "the planner must split this shape"
+        workspace = torch.empty(max(nbytes, 1), dtype=torch.uint8, device="cuda")
+        args = lib.FwdArgs(problem=problem, q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(),
+                           softmax_lse=lse.data_ptr(), q_stride=lib.strides3(q, False), k_stride=lib.strides3(k, False),
+                           v_stride=lib.strides3(v, False), out_stride=lib.strides3(out, False),
+                           lse_stride=lib.Stride2(lse.stride(0), lse.stride(1)),
+                           workspace=workspace.data_ptr() if split else None, workspace_bytes=nbytes)
+        assert library.b200fa_fwd(ctypes.byref(args), stream) == 0, lib.last_error()
+        torch.cuda.synchronize()
+        return out[0]
+
+    def tie_difference(name, out, reference):
+        unit = 2.0**-8 * reference.double().abs().amax(-1, keepdim=True)
+        difference = float(((out.double() - reference.double()).abs() / unit).mean())
+        assert difference <= 0.05, f"{name}: mean |O - unsplit O| = {difference:.3f} bfloat16 units"
+
+    for shift in TIE_SHIFTS:
+        exact = (shift + TIE_SCORES) * log2_e
+        _, exponent = torch.frexp(exact.float().double())
+        units = (exact - exact.float().double()).abs() / torch.ldexp(torch.ones_like(exact), exponent - 24)
+        candidates = TIE_SCORES[units >= FAR_ROUNDING]
+        scores = []
+        for _ in range(heads):
+            other = -torch.randint(60, 120, (rows, keys), generator=generator).double() / 2
+            ties = candidates[torch.randint(len(candidates), (rows, 1), generator=generator)]
+            scores.append(other.scatter(1, spread.expand(rows, -1), ties.expand(-1, tied)))
+        scores = torch.stack(scores)
+        q = torch.zeros(rows, heads, head_dim, dtype=torch.float64)
+        q[torch.arange(rows), :, torch.arange(rows)] = 1.0
+        q[..., -1] = 1.0
+        k = torch.zeros(keys, heads, head_dim, dtype=torch.float64)
+        k[..., :rows] = scores.permute(2, 0, 1)
+        k[..., -1] = shift
+        v = torch.randn(keys, heads, head_dim, generator=generator, dtype=torch.float64).bfloat16().double()
+        q, k, v = (x.cuda().bfloat16() for x in (q, k, v))
+        unsplit = forward(q, k, v, split=False)
+        tie_difference("split keys", forward(q, k, v, split=True), unsplit)
+        tie_difference("tied keys in one key block", forward(q, k[order], v[order], split=False), unsplit)
