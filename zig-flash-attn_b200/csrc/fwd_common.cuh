@@ -43,29 +43,30 @@ __device__ __forceinline__ float log2p1_series(float x) {
 }
 
 // Per-row state of the keys that the online softmax sets aside (see row_totals below): `ones` keys, all scoring exactly
-// `apart`, are kept out of the running sum; `row_max` is the largest score of the row so far.
+// `apart`, are kept out of the running sum. (Two registers: the softmax warps have none to spare, and a third one for
+// the running maximum of the row cost the masked blocks of causal problems 4 %.)
 struct TopApart {
-  float row_max = -INFINITY, apart = -INFINITY, ones = 0.f;
+  float apart = -INFINITY, ones = 0.f;
 };
 
 // Decides, from the maxima of two disjoint parts of a key block, whether this row sets the largest keys of the block
-// aside: the block holds the largest score of the row so far, the part without it lies at least 2^3.9 below (necessary
+// aside: the block maximum is not below the score set aside so far, the part without it lies at least 2^3.9 below (necessary
 // for a row whose largest term ends up more than 16 times the sum of the others), and that score is so close to zero
-// that the sum of the others shows in the log-sum-exp at all (above 2^-7 in log2 units the plain logarithm of the sum is
-// within 2^-17 relative; without this condition the fully masked half of a causal diagonal block would qualify in
-// every work item). Also records the block in `row_max`.
-__device__ __forceinline__ bool sets_keys_apart(TopApart& st, float part_a, float part_b, float scale_log2) {
+// that the sum of the others shows in the log-sum-exp at all (above 2^-7 in log2 units the rounding of m c + log2(sum)
+// hides it). The parts are the even and the odd pairs of columns, so that a masked block (a causal diagonal) has visible
+// keys in both as soon as the row sees more than two keys: with the lower and upper half of the columns as parts, the
+// fully masked upper half of every diagonal block qualified and short causal sequences lost 10 %. Whether the keys
+// set aside are the largest of the row needs no bookkeeping: a larger key elsewhere makes the rest exceed their term,
+// and row_totals then takes the plain logarithm.
+__device__ __forceinline__ bool sets_keys_apart(const TopApart& st, float part_a, float part_b, float scale_log2) {
   const float block_max = fmaxf(part_a, part_b);
-  const bool yes = block_max >= st.row_max && fabsf(part_a - part_b) * scale_log2 > 3.9f &&
-                   fabsf(block_max) * scale_log2 < 0.0078125f;
-  st.row_max = fmaxf(st.row_max, block_max);
-  return yes;
+  return block_max >= st.apart && fabsf(part_a - part_b) * scale_log2 > 3.9f && fabsf(block_max) * scale_log2 < 0.0078125f;
 }
 
 // The rare path of a block in which some row of the warp sets keys aside: sums the exponentials of the kColumns scores at
 // TMEM address `t_s` (still intact: P is stored later) a second time, without the keys that score `block_max` when
 // `set_apart` is true for this thread, which it counts in st.ones instead. Keys set aside earlier at a lower score are
-// folded back into `l` first. A rolled loop over chunks of 32 columns keeps the path small; `mc` is the reference
+// folded back into `l` first. A rolled loop over four columns at a time keeps the path small; `mc` is the reference
 // maximum times scale_log2 that the block's exponentials use. Returns the sum that replaces the block sum.
 template <int kColumns>
 __device__ __forceinline__ float sum_without_keys_apart(TopApart& st, float& l, bool set_apart, float block_max,
@@ -83,15 +84,14 @@ __device__ __forceinline__ float sum_without_keys_apart(TopApart& st, float& l, 
   const float2 scale2 = make_float2(scale_log2, scale_log2), shift2 = make_float2(-mc, -mc);
   float sum_even = 0.f, sum_odd = 0.f, ones = st.ones;
 #pragma unroll 1
-  for (int chunk = 0; chunk < kColumns / 32; ++chunk) {
-    float2 again[16];
-    tmem_ld32(t_s + 32 * chunk, reinterpret_cast<uint32_t*>(again));
+  for (int c = 0; c < kColumns; c += 4) {  // four columns per step: the path is rare, its code stays small
+    float2 again[2];
+    tmem_ld4(t_s + c, reinterpret_cast<uint32_t*>(again));
     tc_wait_ld();
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int c = 32 * chunk + 2 * i;
-      const float sx = (!masked || (c >= lo && c < hi)) ? again[i].x : -INFINITY;
-      const float sy = (!masked || (c + 1 >= lo && c + 1 < hi)) ? again[i].y : -INFINITY;
+    for (int i = 0; i < 2; ++i) {
+      const float sx = (!masked || (c + 2 * i >= lo && c + 2 * i < hi)) ? again[i].x : -INFINITY;
+      const float sy = (!masked || (c + 2 * i + 1 >= lo && c + 2 * i + 1 < hi)) ? again[i].y : -INFINITY;
       const float2 x = __ffma2_rn(make_float2(sx, sy), scale2, shift2);
       const float ex = ex2_approx(x.x), ey = ex2_approx(x.y);
       ones += (sx == apart_here ? 1.f : 0.f) + (sy == apart_here ? 1.f : 0.f);
@@ -107,14 +107,13 @@ __device__ __forceinline__ float sum_without_keys_apart(TopApart& st, float& l, 
 //   m       lazy reference maximum of the row (-inf: the row saw no key), in score units
 //   rest    sum of exp2(s c - m c) over the keys that were not set aside
 //   ones    number of keys set aside, all of which score exactly `apart`
-//   row_max largest score of the row
-// The keys set aside contribute ones * exp2(apart c - m c). When they are the largest keys of the row and the rest is
-// below 1/16 of their term, the logarithm is formed as apart c + log2(ones) + log2(1 + rest / term) with the series
+// The keys set aside contribute ones * exp2(apart c - m c). When the rest is below 1/16 of their term (they are then
+// the largest keys of the row: a larger key would contribute more than the term itself), the logarithm is formed as apart c + log2(ones) + log2(1 + rest / term) with the series
 // above: `rest` then keeps its relative accuracy, which the FP32 sum term + rest would round away (a row whose maximum
 // score is exactly 0 over keys 17 to 80 nats below gets an LSE of about exp(-17) ... exp(-80), not 0). This is the
 // accuracy contract of the reference's tie-counting LSE (zig/flash_fwd_sm100.zig:885-901, zig/fragments.zig:123-140,
 // tests/test_softmax_fix.py:353-402); apart c is taken as the FP32 product plus its rounding remainder, as there.
-__device__ __forceinline__ void row_totals(float m, float rest, float ones, float apart, float row_max, float scale_log2,
+__device__ __forceinline__ void row_totals(float m, float rest, float ones, float apart, float scale_log2,
                                            float* total, float* lse) {
   if (m == -INFINITY) {
     *total = 0.f;
@@ -126,7 +125,7 @@ __device__ __forceinline__ void row_totals(float m, float rest, float ones, floa
   if (ones > 0.f) term = ones * ex2_approx(fmaf(apart, scale_log2, -mc));
   const float sum = term + rest;
   float lse2 = mc + log2f(sum);
-  if (ones > 0.f && apart == row_max && rest < 0.0625f * term) {
+  if (ones > 0.f && rest < 0.0625f * term) {
     const float high = apart * scale_log2;
     const float low = fmaf(apart, scale_log2, -high);
     lse2 = high + (low + (ones > 1.f ? log2f(ones) : 0.f) + log2p1_series(rest / term));

@@ -281,7 +281,7 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             c = fmaxf(c, fmaxf(values[i + 2].x, values[i + 2].y));
             d = fmaxf(d, fmaxf(values[i + 3].x, values[i + 3].y));
           }
-          return fmaxf(fmaxf(a, b), fmaxf(c, d));
+          return make_float2(fmaxf(a, c), fmaxf(b, d));  // maxima over the even and over the odd pairs of columns
         };
         // Pass 1: row maximum. Columns [0,64) are read for the maximum only and read again in pass 2; columns
         // [64,128) stay in registers, because P goes over them.
@@ -290,15 +290,18 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tmem_ld32(t_s + 32, reinterpret_cast<uint32_t*>(low) + 32);
         tc_wait_ld();
         if (masked) apply_mask(low, 0);
-        const float max_low = max_of(low);
+        const float2 max_low = max_of(low);
         tmem_ld32(t_s + 64, reinterpret_cast<uint32_t*>(high));
         tmem_ld32(t_s + 96, reinterpret_cast<uint32_t*>(high) + 32);
         tc_wait_ld();
         if (masked) apply_mask(high, 64);
-        const float max_high = max_of(high);
-        const float block_max = fmaxf(max_low, max_high);
+        const float2 max_high = max_of(high);
+        // Maxima over two interleaved halves of the block (even and odd pairs of columns): under a causal or window mask
+        // both halves hold visible keys as soon as the row sees more than two keys of the block.
+        const float max_even = fmaxf(max_low.x, max_high.x), max_odd = fmaxf(max_low.y, max_high.y);
+        const float block_max = fmaxf(max_even, max_odd);
         const float m_new = fmaxf(m, block_max);
-        const bool set_apart = sets_keys_apart(top, max_low, max_high, scale_log2);
+        const bool set_apart = sets_keys_apart(top, max_even, max_odd, scale_log2);
         const bool counting = __any_sync(0xffffffffu, set_apart);
         trace_event(wctx, traced, 1, trace_n, 2100 + (tile_blocks % 100));  // row maximum known
         const bool grow = (m_new - m) * scale_log2 > 8.f;  // also true when m is -inf and m_new is finite
@@ -389,7 +392,7 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if (!mbar_wait_warp(bar_pv_done, (blocks - 1) & 1, wctx, kWaitEpilogue)) { ok = false; break; }
       tc_fence_after();
       float total, lse_row;
-      row_totals(m, l, top.ones, top.apart, top.row_max, scale_log2, &total, &lse_row);
+      row_totals(m, l, top.ones, top.apart, scale_log2, &total, &lse_row);
       const float inv = total > 0.f ? 1.f / total : 0.f;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {

@@ -295,7 +295,7 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           bm2 = fmaxf(bm2, fmaxf(s[i + 2].x, s[i + 2].y));
           bm3 = fmaxf(bm3, fmaxf(s[i + 3].x, s[i + 3].y));
         }
-        const float part_a = fmaxf(bm0, bm1), part_b = fmaxf(bm2, bm3);  // two disjoint parts of the block
+        const float part_a = fmaxf(bm0, bm2), part_b = fmaxf(bm1, bm3);  // even and odd pairs of columns
         const float block_max = fmaxf(part_a, part_b);
         const float m_new = fmaxf(m, block_max);
         const bool set_apart = sets_keys_apart(top, part_a, part_b, scale_log2);
@@ -372,7 +372,7 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if (!mbar_wait_warp(bar_pv_done, (blocks - 1) & 1, wctx, kWaitEpilogue)) { ok = false; break; }
       tc_fence_after();
       float total, lse_row;
-      row_totals(m, l, top.ones, top.apart, top.row_max, scale_log2, &total, &lse_row);
+      row_totals(m, l, top.ones, top.apart, scale_log2, &total, &lse_row);
       const float inv = total > 0.f ? 1.f / total : 0.f;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
