@@ -41,12 +41,15 @@ struct FwdConfig {
   static constexpr int kTmemO = 256;
 };
 
-template <int D>
+template <int D, bool kSplit>
 __global__ void __launch_bounds__(FwdConfig<D>::kThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
            const __grid_constant__ CUtensorMap map_v, const __grid_constant__ FwdParams p) {
   using Cfg = FwdConfig<D>;
   constexpr int NS = Cfg::kStages;
+  // Shares of the key blocks per tile (split-KV). The unsplit instance folds the divisions by it and the partial-result
+  // epilogue away: with both in one kernel, problems of 512-2048 tokens lost 4-8 % to the code they never run.
+  const int splits = kSplit ? p.splits : 1;
   // Register split between the warpgroups: 2 x 128 x 200 + 128 x 104 = 64512, the 384 x 168 registers the CTA is
   // launched with (setmaxnreg only moves registers inside that pool). With 208 / 88 the MMA and TMA warps spilled.
   constexpr int kRegsSoftmax = 200, kRegsOther = 104;
@@ -144,11 +147,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       };
       uint32_t drawn = 0;
       for (int tile; ok && (tile = tiles.push(drawn, p.tile_counter, p.num_tiles, wctx)) >= 0;) {
-        FwdTile t = decode_tile(p, tile / p.splits);
+        FwdTile t = decode_tile(p, tile / splits);
         if (!t.valid) continue;
         KeyCursor cur;
         cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + (kFwdTileM >> p.pack_shift), t.s.lq));
-        if (p.splits > 1) cur.restrict_to_share(tile % p.splits, p.splits);
+        if (kSplit) cur.restrict_to_share(tile % splits, splits);
         OtherBlock kb;
         if (!cur.next(&kb)) continue;
         if (!mbar_wait(bar_q_empty, (q_count & 1) ^ 1, wctx, kWaitQEmpty)) { ok = false; break; }
@@ -214,11 +217,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       };
       uint32_t popped = 0;
       for (int tile; ok && (tile = tiles.pop_thread(popped, wctx)) >= 0;) {
-        FwdTile t = decode_tile(p, tile / p.splits);
+        FwdTile t = decode_tile(p, tile / splits);
         if (!t.valid) continue;
         KeyCursor cur;
         cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + (kFwdTileM >> p.pack_shift), t.s.lq));
-        if (p.splits > 1) cur.restrict_to_share(tile % p.splits, p.splits);
+        if (kSplit) cur.restrict_to_share(tile % splits, splits);
         OtherBlock kb;
         if (!cur.next(&kb)) continue;
         const uint32_t q_phase = q_count & 1;
@@ -293,7 +296,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     bool ok = true;
     uint32_t popped = 0;
     for (int tile; ok && (tile = tiles.pop_warp(popped, wctx)) >= 0;) {
-      FwdTile t = decode_tile(p, tile / p.splits);
+      FwdTile t = decode_tile(p, tile / splits);
       if (!t.valid) continue;
       // Row within the sequence and head of this thread (packed heads: tile row = token << pack_shift | head of group).
       const int tile_row = stage * kBlockM + row_in_stage;
@@ -301,8 +304,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       const int head = t.head + (tile_row & ((1 << p.pack_shift) - 1));
       KeyCursor cur;
       cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + (kFwdTileM >> p.pack_shift), t.s.lq));
-      const int split = p.splits > 1 ? tile % p.splits : 0;
-      if (p.splits > 1) cur.restrict_to_share(split, p.splits);
+      const int split = kSplit ? tile % splits : 0;
+      if (kSplit) cur.restrict_to_share(split, splits);
       const int band_lo = cur.band.lo(row), band_hi = cur.band.hi(row);
       // Row state: `m` is the lazy reference maximum, `l` the sum of the exponentials relative to it of every key except
       // the keys set aside (TopApart, fwd_common.cuh: the tie-counting LSE of the reference,
@@ -464,7 +467,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       float* lse_ptr = p.lse + t.s.batch_coord * p.lse_batch_stride + (int64_t)head * p.lse_head_stride + t.s.q0 + row;
       // Split-KV: this share's normalised output (fp32) and log-sum-exp go to the partial buffers instead.
       float* o_part = nullptr;
-      if (p.splits > 1) {
+      if (kSplit) {
         const int64_t global_row = (int64_t)t.s.batch_coord * pr.seqlen_q + row;
         o_part = p.o_partial + (((int64_t)split * p.partial_rows + global_row) * pr.heads_q + head) * p.head_dim;
         lse_ptr = p.lse_partial + ((int64_t)split * pr.heads_q + head) * p.partial_rows + global_row;
@@ -756,9 +759,6 @@ static int launch_fwd_d(const b200fa_fwd_args& a, cudaStream_t stream) {
   int status = prepare_forward(a, stream, D, kFwdTileM, kBlockN, &p, &map_q, &map_k, &map_v, &nothing_to_do, 0,
                                pack_shift_of(a.problem));
   if (status != B200FA_OK || nothing_to_do) return status;
-  static bool attribute_set[64] = {false};
-  status = set_dynamic_smem_once(reinterpret_cast<const void*>(&fwd_kernel<D>), Cfg::kSmemBytes, attribute_set);
-  if (status != B200FA_OK) return status;
   int sms = 0;
   status = device_sm_count(&sms);
   if (status != B200FA_OK) return status;
@@ -776,7 +776,17 @@ static int launch_fwd_d(const b200fa_fwd_args& a, cudaStream_t stream) {
     p.num_tiles *= plan.splits;
   }
   const int grid = p.num_tiles < sms ? p.num_tiles : sms;
-  fwd_kernel<D><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+  if (split) {
+    static bool attribute_set[64] = {false};
+    status = set_dynamic_smem_once(reinterpret_cast<const void*>(&fwd_kernel<D, true>), Cfg::kSmemBytes, attribute_set);
+    if (status != B200FA_OK) return status;
+    fwd_kernel<D, true><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+  } else {
+    static bool attribute_set[64] = {false};
+    status = set_dynamic_smem_once(reinterpret_cast<const void*>(&fwd_kernel<D, false>), Cfg::kSmemBytes, attribute_set);
+    if (status != B200FA_OK) return status;
+    fwd_kernel<D, false><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+  }
   B200FA_CUDA_CHECK(cudaGetLastError());
   if (split) {
     const int64_t threads = p.partial_rows * bp.heads_q * (bp.head_dim / 4);
