@@ -146,7 +146,11 @@ struct OtherBlock {
 // Fixed length / varlen: one banded run (the sequence's own keys). Inter-sequence: every maximal run of visible key
 // sequences is a dense run of contiguous key rows, except that the query's own key sequence is a banded run of its
 // own when a window or causal bound applies to it.
-struct KeyCursor {
+// kBits = false compiles the visibility-bit scan out (problems without bits: fixed length and plain packed batches);
+// the forward kernel at head_dim <= 128 has an instance of its own for them, because the scan code inlined into its
+// three roles costs short sequences a few percent even when it never runs.
+template <bool kBits>
+struct KeyCursorT {
   const Problem* p;
   int seq, m0, m1;
   Band band;       // band of the sequence itself
@@ -171,7 +175,7 @@ struct KeyCursor {
       scan = -1;
       return;
     }
-    if (!p->bits) {
+    if (!kBits || !p->bits) {
       scan = -1;
       run_row0 = s.k0;
       run_len = s.lk;
@@ -239,7 +243,7 @@ struct KeyCursor {
 
   B200FA_HD bool next(OtherBlock* out) {
     if (blk >= blk_end) {
-      if (scan < 0 || !next_run()) return false;
+      if (!kBits || scan < 0 || !next_run()) return false;
     }
     out->row = run_row0 + blk * kBlockN;
     out->col0 = blk * kBlockN;
@@ -250,9 +254,14 @@ struct KeyCursor {
   }
 };
 
+using KeyCursor = KeyCursorT<true>;
+
 // Mirror of KeyCursor for the backward pass: walks the query blocks (kBlockM rows) that can see the key columns
 // [c0, c1) of key sequence `seq`, in increasing query order. Uses the transposed visibility bits.
-struct QueryCursor {
+// kBits = false compiles the scan of the transposed visibility bits out. The backward kernels use the full cursor:
+// an instance without the scan measured 1-3 % slower there, unlike in the forward kernel.
+template <bool kBits>
+struct QueryCursorT {
   const Problem* p;
   int seq, c0, c1;
   Band band;
@@ -277,7 +286,7 @@ struct QueryCursor {
       scan = -1;
       return;
     }
-    if (!p->bits_t) {
+    if (!kBits || !p->bits_t) {
       scan = -1;
       run_row0 = s.q0;
       run_len = s.lq;
@@ -335,7 +344,7 @@ struct QueryCursor {
 
   B200FA_HD bool next(OtherBlock* out) {
     if (blk >= blk_end) {
-      if (scan < 0 || !next_run()) return false;
+      if (!kBits || scan < 0 || !next_run()) return false;
     }
     out->row = run_row0 + blk * kBlockM;
     out->col0 = blk * kBlockM;
@@ -345,6 +354,7 @@ struct QueryCursor {
     return true;
   }
 };
+using QueryCursor = QueryCursorT<true>;
 
 // Number of entries of a work list over `rows` packed rows in `batch` sequences with `block` rows per entry
 // (upper bound that needs no knowledge of the individual lengths): reference src/zigfa/_impl/tensors.py:79-84.

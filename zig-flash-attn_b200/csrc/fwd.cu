@@ -41,7 +41,7 @@ struct FwdConfig {
   static constexpr int kTmemO = 256;
 };
 
-template <int D, bool kSplit>
+template <int D, bool kSplit, bool kBits>
 __global__ void __launch_bounds__(FwdConfig<D>::kThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
            const __grid_constant__ CUtensorMap map_v, const __grid_constant__ FwdParams p) {
@@ -149,7 +149,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       for (int tile; ok && (tile = tiles.push(drawn, p.tile_counter, p.num_tiles, wctx)) >= 0;) {
         FwdTile t = decode_tile(p, tile / splits);
         if (!t.valid) continue;
-        KeyCursor cur;
+        KeyCursorT<kBits> cur;
         cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + (kFwdTileM >> p.pack_shift), t.s.lq));
         if (kSplit) cur.restrict_to_share(tile % splits, splits);
         OtherBlock kb;
@@ -219,7 +219,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       for (int tile; ok && (tile = tiles.pop_thread(popped, wctx)) >= 0;) {
         FwdTile t = decode_tile(p, tile / splits);
         if (!t.valid) continue;
-        KeyCursor cur;
+        KeyCursorT<kBits> cur;
         cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + (kFwdTileM >> p.pack_shift), t.s.lq));
         if (kSplit) cur.restrict_to_share(tile % splits, splits);
         OtherBlock kb;
@@ -302,7 +302,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       const int tile_row = stage * kBlockM + row_in_stage;
       const int row = t.m0 + (tile_row >> p.pack_shift);
       const int head = t.head + (tile_row & ((1 << p.pack_shift) - 1));
-      KeyCursor cur;
+      KeyCursorT<kBits> cur;
       cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + (kFwdTileM >> p.pack_shift), t.s.lq));
       const int split = kSplit ? tile % splits : 0;
       if (kSplit) cur.restrict_to_share(split, splits);
@@ -776,17 +776,22 @@ static int launch_fwd_d(const b200fa_fwd_args& a, cudaStream_t stream) {
     p.num_tiles *= plan.splits;
   }
   const int grid = p.num_tiles < sms ? p.num_tiles : sms;
+  // Three instances: split-KV, problems with visibility bits (inter-sequence batches), and the plain one.
+  auto launch = [&](auto kernel, bool (&attribute_set)[64]) -> int {
+    const int set = set_dynamic_smem_once(reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes, attribute_set);
+    if (set != B200FA_OK) return set;
+    kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+    return B200FA_OK;
+  };
+  static bool set_split[64] = {false}, set_bits[64] = {false}, set_plain[64] = {false};
   if (split) {
-    static bool attribute_set[64] = {false};
-    status = set_dynamic_smem_once(reinterpret_cast<const void*>(&fwd_kernel<D, true>), Cfg::kSmemBytes, attribute_set);
-    if (status != B200FA_OK) return status;
-    fwd_kernel<D, true><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+    status = launch(&fwd_kernel<D, true, false>, set_split);
+  } else if (bp.visibility_bits) {
+    status = launch(&fwd_kernel<D, false, true>, set_bits);
   } else {
-    static bool attribute_set[64] = {false};
-    status = set_dynamic_smem_once(reinterpret_cast<const void*>(&fwd_kernel<D, false>), Cfg::kSmemBytes, attribute_set);
-    if (status != B200FA_OK) return status;
-    fwd_kernel<D, false><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+    status = launch(&fwd_kernel<D, false, false>, set_plain);
   }
+  if (status != B200FA_OK) return status;
   B200FA_CUDA_CHECK(cudaGetLastError());
   if (split) {
     const int64_t threads = p.partial_rows * bp.heads_q * (bp.head_dim / 4);

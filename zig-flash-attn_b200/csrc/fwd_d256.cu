@@ -32,6 +32,7 @@ constexpr int kTmemO = 256;
 static_assert(kSmemBytes <= 232448, "shared memory exceeds the per-CTA limit");
 }  // namespace d256
 
+template <bool kBits>  // false: no visibility bits, the scan of the key cursor is compiled out (see KeyCursorT)
 __global__ void __launch_bounds__(d256::kThreads, 1)
 fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ FwdParams p) {
@@ -88,7 +89,7 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   // Number of key blocks of a work item (every role needs it to know where the pipeline ends).
   auto count_blocks = [&](const FwdTile& t) {
-    KeyCursor cur;
+    KeyCursorT<kBits> cur;
     cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kBlockM, t.s.lq));
     OtherBlock kb;
     int n = 0;
@@ -136,7 +137,7 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (!t.valid) continue;
         const int n_blocks = count_blocks(t);
         if (n_blocks == 0) continue;
-        KeyCursor cur_k, cur_v;
+        KeyCursorT<kBits> cur_k, cur_v;
         cur_k.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kBlockM, t.s.lq));
         cur_v.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kBlockM, t.s.lq));
         OtherBlock kb;
@@ -239,7 +240,7 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       FwdTile t = decode_tile(p, tile, kBlockM);
       if (!t.valid) continue;
       const int row = t.m0 + row_in_tile;
-      KeyCursor cur;
+      KeyCursorT<kBits> cur;
       cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kBlockM, t.s.lq));
       const int band_lo = cur.band.lo(row), band_hi = cur.band.hi(row);
       float m = -INFINITY, l = 0.f;
@@ -432,14 +433,21 @@ int launch_fwd_256(const b200fa_fwd_args& a, cudaStream_t stream) {
   bool nothing_to_do = false;
   int status = prepare_forward(a, stream, d256::D, kBlockM, kBlockN, &p, &map_q, &map_k, &map_v, &nothing_to_do, 64);
   if (status != B200FA_OK || nothing_to_do) return status;
-  static bool attribute_set[64] = {false};
-  status = set_dynamic_smem_once(reinterpret_cast<const void*>(&fwd_d256_kernel), d256::kSmemBytes, attribute_set);
-  if (status != B200FA_OK) return status;
   int sms = 0;
   status = device_sm_count(&sms);
   if (status != B200FA_OK) return status;
   const int grid = p.num_tiles < sms ? p.num_tiles : sms;
-  fwd_d256_kernel<<<grid, d256::kThreads, d256::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+  if (a.problem.visibility_bits) {
+    static bool attribute_set[64] = {false};
+    status = set_dynamic_smem_once(reinterpret_cast<const void*>(&fwd_d256_kernel<true>), d256::kSmemBytes, attribute_set);
+    if (status != B200FA_OK) return status;
+    fwd_d256_kernel<true><<<grid, d256::kThreads, d256::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+  } else {
+    static bool attribute_set[64] = {false};
+    status = set_dynamic_smem_once(reinterpret_cast<const void*>(&fwd_d256_kernel<false>), d256::kSmemBytes, attribute_set);
+    if (status != B200FA_OK) return status;
+    fwd_d256_kernel<false><<<grid, d256::kThreads, d256::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+  }
   B200FA_CUDA_CHECK(cudaGetLastError());
   return B200FA_OK;
 }
