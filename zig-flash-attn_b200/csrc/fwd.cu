@@ -724,6 +724,15 @@ int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim,
     p.m_blocks = ceil_div(bp.seqlen_q, tile_rows >> p.pack_shift);
     p.num_tiles = p.m_blocks * bp.batch * (bp.heads_q >> p.pack_shift);
   }
+  p.ratio = bp.heads_kv > 0 ? bp.heads_q / bp.heads_kv : 1;
+  {
+    const int group = p.pack_shift ? 1 : p.ratio;
+    p.div_per_group = FastDiv::make((uint32_t)(p.m_blocks * group));
+    p.div_group = FastDiv::make((uint32_t)group);
+    p.div_heads_kv = FastDiv::make((uint32_t)bp.heads_kv);
+    p.div_heads_q = FastDiv::make((uint32_t)bp.heads_q);
+    p.div_ratio = FastDiv::make((uint32_t)p.ratio);
+  }
   if (p.num_tiles <= 0 || rows_q == 0) return B200FA_OK;
 
   int status = encode_tensor_map(map_q, a.q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, bp.heads_q, rows_q, tensor_batch,

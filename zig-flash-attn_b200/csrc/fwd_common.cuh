@@ -5,6 +5,27 @@
 
 namespace b200fa {
 
+// Division of a non-negative 31-bit number by a divisor that is fixed for a launch: quotient = umulhi(n, mul) >> shift
+// (mul = ceil(2^(31 + ceil_log2 d) / d)), or n itself for d = 1. The work-item decode runs once per item in every warp of
+// the forward kernels; four hardware divisions there are a visible part of the gap between two items.
+struct FastDiv {
+  uint32_t mul, shift, divisor;
+  __host__ __device__ static FastDiv make(uint32_t d) {
+    FastDiv f{0u, 0u, d ? d : 1u};
+    if (f.divisor > 1u) {
+      uint32_t log2 = 0;
+      while ((1u << log2) < f.divisor) ++log2;
+      const uint64_t power = 1ull << (31 + log2);
+      f.mul = static_cast<uint32_t>((power + f.divisor - 1) / f.divisor);
+      f.shift = log2 - 1;
+    }
+    return f;
+  }
+  __device__ __forceinline__ int div(int n) const {
+    return divisor == 1u ? n : static_cast<int>(__umulhi(static_cast<uint32_t>(n), mul) >> shift);
+  }
+};
+
 struct FwdParams {
   Problem prob;
   float scale_log2;
@@ -15,6 +36,10 @@ struct FwdParams {
   int* tile_counter;      // zero at launch; the CTAs draw their work items from it (TileQueue)
   const int2* work_list;  // packed problems: (sequence, block) per entry; null for fixed length
   int m_blocks;           // fixed length: work items per (batch, head)
+  // decode_tile: divisors fixed per launch (work items per key head, per query block, key heads, query heads) and the
+  // query heads per key head
+  FastDiv div_per_group, div_group, div_heads_kv, div_heads_q, div_ratio;
+  int ratio;
   int num_tiles;
   int head_dim;           // columns of the tensors (<= the compiled width; TMA zero-fills the columns in between)
   int* status;            // device status word of the library
@@ -200,7 +225,7 @@ __device__ __forceinline__ FwdTile decode_tile(const FwdParams& p, int tile, int
   FwdTile t;
   const Problem& pr = p.prob;
   if (p.work_list) {
-    int entry = tile / pr.heads_q;
+    int entry = p.div_heads_q.div(tile);
     t.head = tile - entry * pr.heads_q;
     int2 e = p.work_list[entry];
     t.seq = e.x;
@@ -210,18 +235,17 @@ __device__ __forceinline__ FwdTile decode_tile(const FwdParams& p, int tile, int
     // Work items that run at the same time share K and V: all query blocks and query heads of one (batch entry, key
     // head) are consecutive, late (heavy under a causal mask) query blocks first, so the K/V stream they read stays
     // in L2 (reference zig/tile_scheduler.zig:516-669 orders tiles in L2-sized sections for the same reason).
-    const int ratio = pr.heads_q / pr.heads_kv;
-    const int group = p.pack_shift ? 1 : ratio;  // work items per query block and key head
+    const int group = p.pack_shift ? 1 : p.ratio;  // work items per query block and key head
     const int per_group = p.m_blocks * group;
-    const int kv_group = tile / per_group;  // (batch entry, key head)
+    const int kv_group = p.div_per_group.div(tile);  // (batch entry, key head)
     const int rem = tile - kv_group * per_group;
-    const int mb = rem / group;
-    t.seq = kv_group / pr.heads_kv;
-    t.head = (kv_group - t.seq * pr.heads_kv) * ratio + (rem - mb * group);  // packed: the first head of the group
+    const int mb = p.div_group.div(rem);
+    t.seq = p.div_heads_kv.div(kv_group);
+    t.head = (kv_group - t.seq * pr.heads_kv) * p.ratio + (rem - mb * group);  // packed: the first head of the group
     t.m0 = (p.m_blocks - 1 - mb) * (tile_rows >> p.pack_shift);
     t.valid = true;
   }
-  t.kv_head = t.head / (pr.heads_q / pr.heads_kv);
+  t.kv_head = p.div_ratio.div(t.head);
   if (t.valid) t.s = seq_info(pr, t.seq);
   return t;
 }
