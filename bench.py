@@ -713,7 +713,8 @@ def main():
             line["workloads"] = other_workloads(device, peaks)
             line["anchors"] = cudnn_anchors(device, peaks)
             line["device_status"] = lib.library().b200fa_device_status() or status
-        if not options.skip_cpu:
+        if not options.skip_cpu and world == 1:  # the CPU baseline belongs to the one-GPU line (the other ranks of a
+            # multi-GPU launch spin in the closing barrier on the same host cores, which distorts it)
             line["cpu_baseline"] = {k: v for k, v in cpu_sample(workload, 3, 1).items() if k != "seconds_per_step"}
             line["cpu_baseline"]["config0"] = cpu_config0()
         print(json.dumps(line))
