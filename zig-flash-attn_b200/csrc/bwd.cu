@@ -910,9 +910,8 @@ static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
   B200FA_REQUIRE(a.workspace_bytes >= w.total && (w.total == 0 || a.workspace), "backward workspace is too small: need %zu bytes",
                  w.total);
   B200FA_REQUIRE(reinterpret_cast<uintptr_t>(a.workspace) % 256 == 0, "backward workspace must be 256-byte aligned");
-  const int64_t rows_q = bp.seqlen_q, rows_k = bp.seqlen_k;
   if (bp.batch == 0) return B200FA_OK;
-  const bool no_keys = rows_k == 0;
+  const bool no_keys = bp.seqlen_k == 0;
   uint8_t* ws = static_cast<uint8_t*>(a.workspace);
   float* lse_log2 = reinterpret_cast<float*>(ws + w.lse_log2);
   float* dpsum = reinterpret_cast<float*>(ws + w.dpsum);
@@ -923,7 +922,6 @@ static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
   const bool pivots = pivot_ds_enabled() && w.dk_fix_bytes > 0 && w.rows > 0 && w.key_rows > 0;
   int* any_pivot = reinterpret_cast<int*>(ws + w.dk_fix);
   float* dk_fix = reinterpret_cast<float*>(ws + w.dk_fix + 256);
-  const int64_t tensor_batch = packed ? 1 : bp.batch;
 
   RowMap map{bp.cu_seqlens_q, bp.batch, bp.seqlen_q, w.rows, bp.head_dim};
   mark(0, stream);
