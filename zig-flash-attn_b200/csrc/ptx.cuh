@@ -358,6 +358,9 @@ __device__ __forceinline__ float2 ex2_poly2(float2 x) {
   float2 result;
   result.x = __int_as_float(__float_as_int(poly.x) + (__float_as_int(shifted.x) << 23));
   result.y = __int_as_float(__float_as_int(poly.y) + (__float_as_int(shifted.y) << 23));
+  // Exactly zero for masked scores (-inf) and anything else at the clamp: rows without keys must sum to zero.
+  result.x = x.x > -127.f ? result.x : 0.f;
+  result.y = x.y > -127.f ? result.y : 0.f;
   return result;
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
