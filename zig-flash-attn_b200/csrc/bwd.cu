@@ -993,7 +993,11 @@ static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
       heaviest = weight > heaviest ? weight : heaviest;
     }
     const bool uneven = 2 * heaviest * p.n_blocks >= 3 * total_weight;  // heaviest block >= 1.5 x the mean
-    const int64_t wanted = uneven ? kBwdSection : 1;
+    // Short sequences have few key blocks per (batch entry, head slot) pair, so a section of four pairs is a small
+    // share of a wave and the launch ends in a long tail: wider sections there (measured on 16 384 causal tokens, heads
+    // 16/4: seqlen 1024 502 -> 568 TF/s with 16 pairs, seqlen 2048 666 -> 758 with 8; from seqlen 4096 on four is best).
+    const int64_t wide = p.n_blocks <= 8 ? 16 : p.n_blocks <= 16 ? 8 : kBwdSection;
+    const int64_t wanted = uneven ? wide : 1;
     p.section = (int)(groups < wanted ? groups : wanted);
     B200FA_REQUIRE(groups * p.n_blocks < INT_MAX, "too many key blocks for one backward launch");
     grid = dim3((unsigned)(groups * p.n_blocks), 1, 1);
