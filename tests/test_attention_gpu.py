@@ -434,6 +434,58 @@ def test_head_dim_256_two_cta_variant_matches_the_single_cta_kernel(tmp_path):
         assert torch.equal(out, out_pair) and torch.equal(lse, lse_pair), name
 
 
+BACKWARD_PAIR_SCRIPT = """
+import sys, torch
+sys.path.insert(0, sys.argv[1])
+import zigfa
+torch.manual_seed(7)
+results = {}
+def gradients(name, q, k, v, call):
+    q, k, v = (t.requires_grad_() for t in (q, k, v))
+    out = call(q, k, v)
+    dq, dk, dv = torch.autograd.grad(out, (q, k, v), torch.randn_like(out))
+    results[name] = (dq.cpu(), dk.cpu(), dv.cpu())
+for name, (batch, seqlen_q, seqlen_k, heads_q, heads_kv, options) in {
+    "dense": (2, 700, 1000, 4, 2, {}), "causal": (1, 2048, 2048, 4, 1, {"causal": True}), "window": (2, 1023, 1024, 2, 2, {"window_size": (300, 17)}),
+    "short": (3, 100, 3, 2, 1, {}), "one_block": (1, 64, 128, 1, 1, {}), "odd_blocks": (1, 192, 130, 3, 1, {"causal": True}),
+}.items():
+    make = lambda rows, heads: torch.randn(batch, rows, heads, 256, device="cuda", dtype=torch.bfloat16)
+    gradients(name, make(seqlen_q, heads_q), make(seqlen_k, heads_kv), make(seqlen_k, heads_kv),
+              lambda q, k, v: zigfa.flash_attn_func(q, k, v, **options))
+lengths = torch.tensor([0, 300, 1, 513, 128], dtype=torch.int32)
+cu = torch.nn.functional.pad(lengths.cumsum(0), (1, 0)).int().cuda()
+total = int(lengths.sum())
+make = lambda heads: torch.randn(total, heads, 256, device="cuda", dtype=torch.bfloat16)
+gradients("varlen", make(4), make(2), make(2), lambda q, k, v: zigfa.flash_attn_varlen_func(q, k, v, cu, cu, 513, 513, causal=True))
+torch.save(results, sys.argv[2])
+"""
+
+
+def test_head_dim_256_backward_cluster_variant_matches_the_default_kernel(tmp_path):
+    """The head_dim 256 backward that runs the two halves of a key block as a cluster sharing one score computation
+    (B200FA_BWD_D256_PAIR=1, read at the library's first head_dim 256 backward, hence the child processes) accumulates dK
+    and dV over the same BF16 P and dS in the same order as the default kernel and reduces the same dQ partials: the
+    gradients agree to the rounding of the FP32 dQ reductions, whose order differs from run to run in both kernels."""
+    import os
+    import subprocess
+    import sys
+
+    package = str(next(path for path in sys.path if os.path.isdir(os.path.join(path, "zigfa"))))
+    outputs = {}
+    for switch in ("0", "1"):
+        target = tmp_path / f"pair{switch}.pt"
+        env = dict(os.environ, B200FA_BWD_D256_PAIR=switch)
+        done = subprocess.run([sys.executable, "-c", BACKWARD_PAIR_SCRIPT, package, str(target)], env=env, capture_output=True,
+                              text=True, timeout=600)
+        assert done.returncode == 0, done.stderr[-2000:]
+        outputs[switch] = torch.load(target)
+    for name, gradients in outputs["0"].items():
+        for which, default, paired in zip(("dq", "dk", "dv"), gradients, outputs["1"][name]):
+            bound = 2.0**-7 * default.float().abs().max().item() + 1e-6  # two BF16 roundings of the largest element
+            assert (default.float() - paired.float()).abs().max().item() <= bound, (name, which)
+            assert torch.isfinite(paired.float()).all(), (name, which)
+
+
 def test_concurrent_host_threads_on_their_own_streams():
     """The entry points may be called from several host threads at once (per-device caches behind a mutex, a work-item
     counter per launch): four threads, each on its own stream, run forward passes of different shapes in a loop and

@@ -23,29 +23,13 @@
 // buffers.
 // Warps 0-15 compute P and dS (four groups, 16 query columns each), warps 16-23 drain dQ (two groups, 32 query rows
 // each), warp 24 issues MMAs, warp 25 issues the loads.
-#include "bwd_common.cuh"
+#include "bwd_d256_common.cuh"
+
+#include <cstdlib>
 
 namespace b200fa {
 namespace bd256 {
 
-constexpr int kSubM = 64;                   // query rows per iteration
-constexpr int kGroups = 4;                   // compute warpgroups: a thread handles one key row and 64 / kGroups query columns
-constexpr int kCols = kSubM / kGroups;
-constexpr int kComputeWarps = 4 * kGroups;
-constexpr int kDrains = 2;                   // dQ drain warpgroups: each takes half of the 64 query rows of an iteration
-constexpr int kMmaWarp = kComputeWarps + 4 * kDrains, kLoadWarp = kMmaWarp + 1;
-constexpr int kThreads = 32 * (kMmaWarp + 4);
-// registers per thread of the compute, drain and MMA/load warpgroups: 4 x 128 x 88 + 2 x 128 x 56 + 128 x 40 = 896 x 72
-constexpr int kRegsCompute = 88, kRegsDrain = 56, kRegsMisc = 40;
-static_assert(kComputeWarps * 32 * kRegsCompute + kDrains * 128 * kRegsDrain + 128 * kRegsMisc == kThreads * 72,
-              "the per-role register budgets must add up to the launch allocation");
-constexpr int kKvPanel = 128 * 128;         // 128 key rows x 64 columns BF16
-constexpr int kKvBytes = 4 * kKvPanel;      // 64 KB
-constexpr int kQPanel = kSubM * 128;        // 64 query rows x 64 columns BF16
-constexpr int kQBytes = 4 * kQPanel;        // 32 KB
-constexpr int kDsBytes = 128 * 128;         // 128 keys x 64 queries BF16
-constexpr int kStageRows = 16;              // query rows per staging buffer
-constexpr int kStageBytes = kStageRows * 128 * 4;
 constexpr int kOffK = 0;
 constexpr int kOffQ = kOffK + kKvBytes;     // two stages of (Q tile, dO tile): Q0 dO0 Q1 dO1
 constexpr int kStageStride = 2 * kQBytes;
@@ -57,31 +41,6 @@ constexpr int kOffBars = kOffStats + 4 * 256;
 constexpr int kSmemBytes = kOffBars + 192;
 constexpr int kTmemS = 0, kTmemDp = 64, kTmemDv = 128, kTmemDk = 256, kTmemV = 384;
 static_assert(kSmemBytes <= 232448, "shared memory of the head_dim 256 backward kernel exceeds the per-CTA limit");
-
-// Yields the 128-row query blocks of a QueryCursor as 64-row halves (a half past the end of its run is skipped).
-struct HalfBlockCursor {
-  QueryCursor cursor;
-  OtherBlock block;
-  int half;
-  __device__ void init(const Problem* problem, int seq, const SeqInfo& s, int c0, int c1) {
-    cursor.init(problem, seq, s, c0, c1);
-    half = 2;
-  }
-  __device__ bool next(OtherBlock* out) {
-    for (;;) {
-      if (half >= 2) {
-        if (!cursor.next(&block)) return false;
-        half = 0;
-      }
-      const int h = half++;
-      if (block.col0 + h * kSubM >= block.limit) continue;
-      *out = block;
-      out->row = block.row + h * kSubM;
-      out->col0 = block.col0 + h * kSubM;
-      return true;
-    }
-  }
-};
 
 template <bool kPivot>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -126,7 +85,6 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t bar_ds_full = bars + 32, bar_dq_full = bars + 48, bar_dq_empty = bars + 56;
   const uint32_t bar_final = bars + 64, bar_v_ready = bars + 72;
   const uint32_t bar_q_full = bars + 80 /*[2]*/, bar_q_empty = bars + 96 /*[2]*/, bar_do_full = bars + 112 /*[2]*/;
-  const uint32_t bar_do_empty = bars + 128 /*[2]*/;
   const uint32_t tmem_slot = bars + 144, abort_slot = bars + 148, bar_ds_free = bars + 152;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + (abort_slot - base));
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - base));
@@ -142,7 +100,6 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       mbar_init(bar_q_full + 8 * i, 33);
       mbar_init(bar_q_empty + 8 * i, 1);
       mbar_init(bar_do_full + 8 * i, 1);
-      mbar_init(bar_do_empty + 8 * i, 1);
     }
     mbar_init(bar_v_ready, 32 * kComputeWarps);
     mbar_init(bar_s_full, 1);
@@ -218,13 +175,15 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           const int r = lane + 32 * k;
           if (row0 + r < p.rows) {
             // Both row statistics travel with the Q tile: its stage is released by the dK MMA, which comes after the
-            // dS phase has read them (the dO stage is released earlier, by the dV MMA).
+            // dS phase has read them.
             cp_async_4(smem_lse + st * 256 + r * 4, lse_head + row0 + r);
             cp_async_4(smem_dpsum + st * 256 + r * 4, dpsum_head + row0 + r);
           }
         }
         cp_async_arrive_noinc(bar_q_full + 8 * st);
-        if (!mbar_wait(bar_do_empty + 8 * st, phase ^ 1, wctx, kWaitBwdLoad)) { ok = false; break; }
+        // The dO tile of the stage is released with its Q tile (bar_q_empty, waited for above): one commit for both,
+        // because every tcgen05.commit takes a slot of the MMA stream that bounds this kernel (one commit less per
+        // iteration measured +4.5 %).
         if (lane == 0) {
           mbar_expect_tx(bar_do_full + 8 * st, kQBytes);
 #pragma unroll
@@ -287,7 +246,6 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         for (int kk = 0; kk < 4; ++kk)
           umma_ts(t_dv, t_s + kk * kCols, umma_smem_desc(do_half + kk * 2048, kQPanel, 1024), idesc_dv,
                   it > 0 || kk > 0);
-        tc_commit(bar_do_empty + 8 * st);
         // S^T of the next iteration (P^T of this one has been consumed by the MMAs above, which run first)
         if (more) {
           if (!mbar_wait(bar_q_full + 8 * (st ^ 1), ((it + 1) >> 1) & 1, wctx, kWaitBwdMma)) { ok = false; break; }
@@ -616,6 +574,14 @@ int launch_bwd_main_d256(const b200fa_bwd_args& a, const BwdParams& p, dim3 grid
                          cudaStream_t stream) {
   using namespace bd256;
   constexpr int D = 256;
+  // B200FA_BWD_D256_PAIR=1 (read at the first call) runs the two halves of a key block as a cluster that computes the
+  // scores once (bwd_d256_pair.cu), without pivot gradients. It measured 7-9 % slower than the independent CTAs of this
+  // file on full-size problems, so it is not the default.
+  static const bool paired = [] {
+    const char* setting = std::getenv("B200FA_BWD_D256_PAIR");
+    return setting != nullptr && setting[0] == '1';
+  }();
+  if (paired && !p.pivot_key) return launch_bwd_main_d256_pair(a, p, grid, dq_accum, stat_rows, stream);
   const b200fa_problem& bp = a.problem;
   const bool packed = bp.cu_seqlens_q != nullptr;
   const int64_t rows_q = bp.seqlen_q, rows_k = bp.seqlen_k;

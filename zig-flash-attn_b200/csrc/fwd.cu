@@ -55,6 +55,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
            const __grid_constant__ CUtensorMap map_v, const __grid_constant__ FwdParams p) {
   using Cfg = FwdConfig<D>;
   constexpr int NS = Cfg::kStages;
+  // head_dim 64 (24 MMAs and 6 commits per pair of blocks) is bound by the rate of tcgen05 instructions, and handing the
+  // K/V slots back from a softmax thread instead of by a commit gains 1.5-3 % there; at head_dim 128 it changes nothing.
+  constexpr bool kSimtRelease = Cfg::kOwnP;
   // Shares of the key blocks per tile (split-KV). The unsplit instance folds the divisions by it and the partial-result
   // epilogue away: with both in one kernel, problems of 512-2048 tokens lost 4-8 % to the code they never run.
   const int splits = kSplit ? p.splits : 1;
@@ -245,7 +248,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         tc_fence_after();
         issue_s(1, smem_kv + (k_index % NS) * Cfg::kTileBytes);
         tc_commit(bar_s_full + 8);
-        tc_commit(bar_kv_empty + 8 * (k_index % NS));
+        if (!kSimtRelease) tc_commit(bar_kv_empty + 8 * (k_index % NS));
         bool first = true;
         for (;;) {
           const bool more = cur.next(&kb);
@@ -276,11 +279,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
               tc_fence_after();
               issue_s(1, k_smem);
               tc_commit(bar_s_full + 8);
-              tc_commit(bar_kv_empty + 8 * (k_index % NS));
+              if (!kSimtRelease) tc_commit(bar_kv_empty + 8 * (k_index % NS));
             }
             if (!issue_pv(1, v_smem, !first, phase)) { ok = false; break; }
             tc_commit(bar_pv_done + 8);
-            tc_commit(bar_kv_empty + 8 * (v_index % NS));
+            if (!kSimtRelease) tc_commit(bar_kv_empty + 8 * (v_index % NS));
             if (!more) tc_commit(bar_q_empty);
           } else {
             if (!issue_pv(0, v_smem, !first, phase)) { ok = false; break; }
@@ -297,12 +300,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             if (!issue_pv(1, v_smem, !first, phase)) { ok = false; break; }
             if (!more) tc_commit(bar_pv_done + 8);
             trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 1600 + (blocks % 100));  // PV of stage 1 issued
-            tc_commit(bar_kv_empty + 8 * (v_index % NS));
+            if (!kSimtRelease) tc_commit(bar_kv_empty + 8 * (v_index % NS));
             if (more) {
               issue_s(1, k_smem);
               tc_commit(bar_s_full + 8);
               trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 1100 + (blocks % 100));  // S of stage 1 issued
-              tc_commit(bar_kv_empty + 8 * (k_index % NS));
+              if (!kSimtRelease) tc_commit(bar_kv_empty + 8 * (k_index % NS));
             } else {
               tc_commit(bar_q_empty);
             }
@@ -330,6 +333,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     const uint32_t my_pv_done = bar_pv_done + 8 * stage;
     const float scale_log2 = p.scale_log2;
     uint32_t blocks = 0, tiles_done = 0;  // key blocks and work items with key blocks so far
+    // K/V slots are handed back to the load warp by one softmax thread of stage 1 instead of a tcgen05.commit of the MMA
+    // thread: a commit takes a slot in the MMA stream like an MMA does. The scores of block j of stage 1 being present
+    // proves that every MMA issued before them is complete: those on K_j and, for j > 0, those on V_(j-1). The ring
+    // indices mirror the MMA thread's: a work item with n key blocks takes K_0 V_0 K_1 V_1 ... V_(n-1).
+    const bool releaser = kSimtRelease && stage == 1 && (warp & 3) == 0 && lane == 0;
+    uint32_t ring = 0;
     bool ok = true;
     uint32_t popped = 0;
     for (int tile; ok && (tile = tiles.pop_warp(popped, wctx)) >= 0;) {
@@ -353,6 +362,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       OtherBlock kb;
       while (cur.next(&kb)) {
         if (!mbar_wait_traced(my_s_full, blocks & 1, wctx, kWaitSFull, 19, true)) { ok = false; break; }
+        if (releaser) mbar_arrive(bar_kv_empty + 8 * ((ring + 2 * tile_blocks) % NS));
         const long long t_soft = trace_clock(wctx);
         tc_fence_after();
         const bool traced = blockIdx.x == 0 && (threadIdx.x & 127) == 0 && popped == 1;
@@ -414,6 +424,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         // of the barrier is observed here or, for the last block of a work item, in the epilogue.
         if (Cfg::kOwnP && tile_blocks > 0 && !mbar_wait_traced(my_pv_done, (blocks - 1) & 1, wctx, kWaitPvDone, 26, true)) { ok = false; break; }
         if (Cfg::kOwnP && tile_blocks > 0) tc_fence_after();
+        if (releaser && tile_blocks > 0) mbar_arrive(bar_kv_empty + 8 * ((ring + 2 * tile_blocks - 1) % NS));
         // One rarely taken branch, behind one vote, holds both the rescale and the second summation of blocks with keys
         // set aside, so the common path has a single vote and branch between the maximum and the exponentials.
         float sum_counted = 0.f;
@@ -536,6 +547,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       }
       if (!mbar_wait_traced(my_pv_done, (Cfg::kOwnP ? blocks - 1 : tiles_done) & 1, wctx, kWaitEpilogue, 22, true)) { ok = false; break; }
       ++tiles_done;
+      if (releaser) mbar_arrive(bar_kv_empty + 8 * ((ring + 2 * tile_blocks - 1) % NS));
+      ring += 2 * tile_blocks;
       const long long t_epi = trace_clock(wctx);
       tc_fence_after();
       float total, lse_row;

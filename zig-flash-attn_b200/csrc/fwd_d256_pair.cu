@@ -33,25 +33,6 @@ constexpr int kThreads = 256;
 constexpr int kTmemO = 256;
 static_assert(kSmemBytes <= 232448, "shared memory exceeds the per-CTA limit");
 
-__device__ __forceinline__ uint32_t cluster_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// Address of `addr` (a shared-memory address of this CTA) in CTA `rank` of the cluster, in the shared::cluster window.
-__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  // default semantics (release at CTA scope): what is published is TMEM content, ordered by the tcgen05 fences; a
-  // release at cluster scope costs the arriving warp about 1300 cycles
-  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
 // TMA load into this CTA's shared memory whose bytes complete on a barrier given as a shared::cluster address (the
 // leader's).
 __device__ __forceinline__ void tma_load_4d_pair(uint32_t smem_dst, const void* tmap, uint32_t bar_cluster, int c0, int c1,
