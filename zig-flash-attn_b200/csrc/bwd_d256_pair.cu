@@ -31,7 +31,8 @@
 // buffers.
 // Warps 0-15 compute P and dS on owned iterations (four groups, 16 query columns each), warps 16-23 drain dQ (two
 // groups, 32 query rows each), warp 24 issues MMAs, warp 25 issues the loads, warp 26 the copies between the CTAs.
-// No multicast loads; the only traffic between the CTAs is those bulk copies and one tcgen05.commit per iteration onto
+// Every TMA load goes to the shared memory of the CTA that issues it; the only traffic between the CTAs is those bulk
+// copies from shared memory to shared memory and one tcgen05.commit per iteration onto
 // a barrier of the other CTA.
 //
 // Selected by B200FA_BWD_D256_PAIR=1 and not the default: with a third fewer MMA instructions per iteration it runs
