@@ -1,87 +1,64 @@
-// Forward attention kernel for head_dim 512 on sm_100a, built on a head_dim 256 kernel with 64-key blocks (kSplit = 1,
-// kept as the base case of the template; head_dim 256 itself is served by the 128-key kernel of fwd_d256.cu).
+// Forward attention kernel for head_dim 512 on sm_100a with 128-key blocks.
 //
-// With 256 output columns the FP32 accumulator O takes half of TMEM, so there is one query stage: a work item is 128
-// query rows of one head. Keys are taken 64 at a time, and the score tile S (128 x 64) is double-buffered instead:
-//   S(n)   = Q K_n^T     SS-MMA 128x64x256  -> TMEM buffer n & 1, columns [128 b, 128 b + 64)
-//   P(n)                 BF16, columns [128 b + 64, 128 b + 96) of the same buffer (no aliasing with S)
-//   O     += P(n) V_n    TS-MMA 128x256x64  -> TMEM columns [256, 512)
-// The MMA warp issues S(n + 2) right after O += P(n) V_n, so while the softmax warps work on block n + 1 the tensor pipe
-// runs the PV product of block n and the scores of block n + 2. Per block the tensor work (2 x 512 cycles) about equals
-// the softmax work of one warpgroup, which is why one softmax warpgroup is enough here.
+// An accumulator of 512 columns would take all of TMEM, so a work item (128 query rows of one head) is split in two, one
+// CTA per 256 output columns (tile index = 2 * item + half). Both halves compute the full scores (reduction over 512
+// columns) and their own half of P V:
+//   S(n)   = Q K_n^T        SS-MMA 128x128x512 -> TMEM buffer n & 1, columns [128 b, 128 b + 128), in four parts of 128
+//                           reduction columns (one ring slot each)
+//   P(n)                    BF16, over columns [64,128) of the same buffer (whose scores the softmax warps hold in registers)
+//   O_h   += P(n) V_n[:, h] TS-MMA 128x256x128 -> TMEM columns [256, 512), issued in two key halves (one ring slot each)
+// One 128-row query stage with the score tile double-buffered: the MMA warp issues S(n + 2) right after O += P(n) V_n, so
+// the softmax of block n + 1 overlaps the PV product of block n and the scores of block n + 2 (the structure of the
+// head_dim 256 kernel, fwd_d256.cu). An earlier version with 64-key blocks needed twice the tcgen05 instructions for the
+// score product (N = 64 at the cost of N = 128) and was bound by their number: 600 against 830 TF/s on batch 4, seqlen
+// 8192, heads 16/4, causal.
+// Shared memory: Q 128 KB and a ring of three 32 KB slots that carries, in the order the MMA warp consumes them, the
+// four parts of a K block (128 keys x 128 columns each) and the two halves of a V block (64 keys x 256 columns each).
 // Warps 0-3: softmax and epilogue (thread = query row), warp 4: MMA issue, warp 5: TMA loads, warps 6-7: spare.
-//
-// head_dim 512 (kSplit = 2) runs the same kernel: an accumulator of 512 columns would take all of TMEM, so a work
-// item is split in two, one per 256 output columns (tile index = 2 * item + half). Both halves compute the full
-// scores (reduction over 512 columns: a key block is two ring slots) and their own half of P V. The query tile takes
-// 128 KB of shared memory, which leaves three ring slots.
 #include "fwd_common.cuh"
 
 namespace b200fa {
 
-namespace wide {
-constexpr int D = 256;                            // output columns of a CTA; the reduction runs over kSplit * D columns
-constexpr int kSubN = 64;                         // keys per block
-constexpr int kKvBytes = kSubN * D * 2;           // 32 KB: one ring slot (64 keys x 256 columns)
-constexpr int kQPanel = kBlockM * 128;            // 64-column panel of Q
-constexpr int kKvPanel = kSubN * 128;             // 64-column panel of K / V
+namespace d512 {
+constexpr int D = 256;                            // output columns of a CTA
+constexpr int kSplit = 2;                         // CTAs per work item; the reduction runs over kSplit * D columns
+constexpr int kParts = kSplit * D / 128;          // K parts of 128 reduction columns per key block
+constexpr int kSlots = 3;                         // ring slots
+constexpr int kSlotBytes = 32768;                 // a K part (128 keys x 128 columns) or a V half (64 keys x 256 columns)
+constexpr int kQBytes = kBlockM * D * kSplit * 2; // 128 KB
+constexpr int kQPanel = kBlockM * 128;            // 64-column panel of Q (128 rows)
+constexpr int kKPanel = kBlockN * 128;            // 64-column panel of a K part (128 rows)
+constexpr int kVPanel = 64 * 128;                 // 64-column panel of a V half-block (64 rows)
+constexpr int kSmemBytes = kQBytes + kSlots * kSlotBytes + 1024 + 512;
 constexpr int kThreads = 256;
 constexpr int kTmemO = 256;
-template <int kSplit>
-struct Config {
-  static constexpr int kStages = kSplit == 1 ? 5 : 3;            // K/V ring slots
-  static constexpr int kQBytes = kBlockM * D * kSplit * 2;       // 64 KB or 128 KB
-  static constexpr int kSmemBytes = kQBytes + kStages * kKvBytes + 1024 + 256;
-  static_assert(kSmemBytes <= 232448, "shared memory exceeds the per-CTA limit");
-};
-}  // namespace wide
+static_assert(kSmemBytes <= 232448, "shared memory exceeds the per-CTA limit");
+}  // namespace d512
 
-// Yields the key blocks of a KeyCursor as 64-key halves.
-struct SubBlockCursor {
-  KeyCursor cursor;
-  OtherBlock block;
-  int half;
-  __device__ void init(const Problem* problem, int seq, const SeqInfo& s, int m0, int m1) {
-    cursor.init(problem, seq, s, m0, m1);
-    half = 2;
-  }
-  __device__ bool next(OtherBlock* out) {
-    if (half >= 2) {
-      if (!cursor.next(&block)) return false;
-      half = 0;
-    }
-    *out = block;
-    out->row = block.row + half * wide::kSubN;
-    out->col0 = block.col0 + half * wide::kSubN;
-    ++half;
-    return true;
-  }
-};
-
-template <int kSplit>
-__global__ void __launch_bounds__(wide::kThreads, 1)
-fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ FwdParams p) {
-  using namespace wide;
-  constexpr int NS = Config<kSplit>::kStages;
-  constexpr int kQBytes = Config<kSplit>::kQBytes;
-  const int num_tiles = p.num_tiles * kSplit;  // tile = kSplit * work item + half of the output columns
+template <bool kBits>  // false: no visibility bits, the scan of the key cursor is compiled out (see KeyCursorT)
+__global__ void __launch_bounds__(d512::kThreads, 1)
+fwd_d512_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ FwdParams p) {
+  using namespace d512;
+  constexpr int NS = kSlots;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t smem_q = smem_base;
-  const uint32_t smem_kv = smem_base + kQBytes;
-  const uint32_t bars = smem_kv + NS * kKvBytes;
+  const uint32_t smem_ring = smem_q + kQBytes;
+  const uint32_t bars = smem_ring + NS * kSlotBytes;
   const uint32_t bar_q_full = bars, bar_q_empty = bars + 8;
-  const uint32_t bar_kv_full = bars + 16, bar_kv_empty = bar_kv_full + 8 * NS;
-  const uint32_t bar_s_full = bar_kv_empty + 8 * NS;  // [2]
-  const uint32_t bar_p_full = bar_s_full + 16;        // [2]
+  const uint32_t bar_kv_full = bars + 32, bar_kv_empty = bar_kv_full + 8 * NS;  // [NS] each
+  const uint32_t bar_s_full = bar_kv_empty + 8 * NS;                            // [2]
+  const uint32_t bar_p_half = bar_s_full + 16;                               // [2]
+  const uint32_t bar_p_full = bar_p_half + 16;                               // [2]
   const uint32_t bar_pv_done = bar_p_full + 16;
   const uint32_t tmem_slot = bar_pv_done + 8, abort_slot = tmem_slot + 4;
   TileQueue tiles;
-  tiles.place(bars + 160);  // the barriers above end at byte 144 with five ring slots
+  tiles.place(bars + 256);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + (abort_slot - smem_u32(smem_raw)));
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
-  const WaitCtx wctx{abort_flag, p.status, nullptr};
+  const WaitCtx wctx{abort_flag, p.status, p.trace};
+  int trace_n = 0;  // timeline of the first work item of CTA 0 (tuning builds)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -94,6 +71,7 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_s_full + 8 * i, 1);
+      mbar_init(bar_p_half + 8 * i, 128);
       mbar_init(bar_p_full + 8 * i, 128);
     }
     mbar_init(bar_pv_done, 1);
@@ -110,9 +88,9 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t tmem_base = *tmem_ptr_smem;
   const Problem& pr = p.prob;
 
-  // Number of 64-key blocks of a work item (every role needs it to know where the pipeline ends).
+  // Number of key blocks of a work item (every role needs it to know where the pipeline ends).
   auto count_blocks = [&](const FwdTile& t) {
-    SubBlockCursor cur;
+    KeyCursorT<kBits> cur;
     cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kBlockM, t.s.lq));
     OtherBlock kb;
     int n = 0;
@@ -122,35 +100,35 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   if (warp == 5) {
     // ------------------------------------------------------------------ TMA producer
-    // Load order = consumption order of the MMA warp: K0, K1, then V(n), K(n + 2) for n = 0, 1, ...
+    // Load order = consumption order of the MMA warp: the parts of K0 and K1, then V_hi(n), V_lo(n) and the parts of
+    // K(n + 2) for n = 0, 1, ...
     if (lane == 0) {
-      uint32_t ring = 0, q_count = 0;
+      uint32_t ring = 0, q_count = 0, drawn = 0;
       bool ok = true;
-      // One ring slot: 64 rows x 256 columns starting at column col0.
-      auto load_slot = [&](const CUtensorMap* map, int col0, int head, int row, int batch_coord) -> bool {
+      // One ring slot: `panels` 64-column panels of `map` starting at column col0 (K part: 2 panels of 128 rows; V half:
+      // 4 panels of 64 rows; 32 KB either way).
+      auto load_slot = [&](const CUtensorMap* map, int panels, uint32_t panel_bytes, int col0, int head, int row, int batch_coord) -> bool {
         const uint32_t slot = ring % NS, phase = (ring / NS) & 1;
         if (!mbar_wait(bar_kv_empty + 8 * slot, phase ^ 1, wctx, kWaitKvEmpty)) return false;
         const uint32_t bar = bar_kv_full + 8 * slot;
-        mbar_expect_tx(bar, kKvBytes);
-#pragma unroll
-        for (int h = 0; h < 4; ++h)
-          tma_load_4d(smem_kv + slot * kKvBytes + h * kKvPanel, map, bar, col0 + h * 64, head, row, batch_coord);
+        mbar_expect_tx(bar, kSlotBytes);
+        for (int h = 0; h < panels; ++h)
+          tma_load_4d(smem_ring + slot * kSlotBytes + h * panel_bytes, map, bar, col0 + h * 64, head, row, batch_coord);
         ++ring;
         return true;
       };
-      auto load_k = [&](int head, int row, int batch_coord) -> bool {  // all reduction columns: kSplit slots
-        for (int part = 0; part < kSplit; ++part)
-          if (!load_slot(&map_k, part * D, head, row, batch_coord)) return false;
+      auto load_k = [&](int head, int row, int batch_coord) -> bool {
+        for (int part = 0; part < kParts; ++part)
+          if (!load_slot(&map_k, 2, kKPanel, part * 128, head, row, batch_coord)) return false;
         return true;
       };
-      uint32_t drawn = 0;
-      for (int tile; ok && (tile = tiles.push(drawn, p.tile_counter, num_tiles, wctx)) >= 0;) {
+      for (int tile; ok && (tile = tiles.push(drawn, p.tile_counter, p.num_tiles * kSplit, wctx)) >= 0;) {
         FwdTile t = decode_tile(p, tile / kSplit, kBlockM);
         const int dh = tile % kSplit;
         if (!t.valid) continue;
         const int n_blocks = count_blocks(t);
         if (n_blocks == 0) continue;
-        SubBlockCursor cur_k, cur_v;
+        KeyCursorT<kBits> cur_k, cur_v;
         cur_k.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kBlockM, t.s.lq));
         cur_v.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kBlockM, t.s.lq));
         OtherBlock kb;
@@ -166,7 +144,8 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         for (int n = 0; ok && n < n_blocks; ++n) {
           cur_v.next(&kb);
-          ok = load_slot(&map_v, dh * D, t.kv_head, kb.row, t.s.batch_coord);
+          ok = load_slot(&map_v, 4, kVPanel, dh * D, t.kv_head, kb.row + 64, t.s.batch_coord) &&
+               load_slot(&map_v, 4, kVPanel, dh * D, t.kv_head, kb.row, t.s.batch_coord);
           if (ok && n + 2 < n_blocks) {
             cur_k.next(&kb);
             ok = load_k(t.kv_head, kb.row, t.s.batch_coord);
@@ -177,61 +156,68 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   } else if (warp == 4) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc_bf16(kBlockM, kSubN, 0, 0);
+      constexpr uint32_t idesc_s = umma_idesc_bf16(kBlockM, kBlockN, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(kBlockM, D, 0, 1);
-      uint32_t ring = 0, q_count = 0, blocks = 0;  // blocks: PV products issued so far (all work items)
+      uint32_t ring = 0, q_count = 0, popped = 0;
       uint32_t p_phase[2] = {0, 0};
       bool ok = true;
-      auto wait_kv = [&](uint32_t index) -> bool {
-        return mbar_wait(bar_kv_full + 8 * (index % NS), (index / NS) & 1, wctx, kWaitKvFull);
-      };
-      // S = Q K^T over the kSplit ring slots of a key block; each slot is released as soon as its MMAs are issued.
+      // S = Q K^T into score buffer `buffer`: four parts of 128 reduction columns, each from the next ring slot, which is
+      // released as soon as its MMAs are issued.
       auto issue_s = [&](int buffer) -> bool {
-        for (int part = 0; part < kSplit; ++part) {
-          const uint32_t k_index = ring++;
-          if (!wait_kv(k_index)) return false;
+        for (int part = 0; part < kParts; ++part) {
+          const uint32_t slot = ring % NS, phase = (ring / NS) & 1;
+          if (!mbar_wait(bar_kv_full + 8 * slot, phase, wctx, kWaitKvFull)) return false;
+          ++ring;
           tc_fence_after();
-          const uint32_t k_smem = smem_kv + (k_index % NS) * kKvBytes;
-          const uint32_t q_smem = smem_q + part * 4 * kQPanel;
+          const uint32_t k_smem = smem_ring + slot * kSlotBytes;
+          const uint32_t q_smem = smem_q + 2 * part * kQPanel;
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
+          for (int kk = 0; kk < 8; ++kk) {
             umma_ss(tmem_base + buffer * 128, umma_smem_desc(q_smem + (kk >> 2) * kQPanel + (kk & 3) * 32, 16, 1024),
-                    umma_smem_desc(k_smem + (kk >> 2) * kKvPanel + (kk & 3) * 32, 16, 1024), idesc_s, part > 0 || kk > 0);
+                    umma_smem_desc(k_smem + (kk >> 2) * kKPanel + (kk & 3) * 32, 16, 1024), idesc_s, part > 0 || kk > 0);
           }
-          tc_commit(bar_kv_empty + 8 * (k_index % NS));
+          tc_commit(bar_kv_empty + 8 * slot);
         }
         tc_commit(bar_s_full + 8 * buffer);
         return true;
       };
-      uint32_t popped = 0;
+      // O += P[:, 64 h .. 64 h + 64) V_half: the next slot of the ring holds those 64 keys.
+      auto issue_pv_half = [&](int buffer, int half, bool accumulate) -> bool {
+        const uint32_t slot = ring % NS, phase = (ring / NS) & 1;
+        if (!mbar_wait(bar_kv_full + 8 * slot, phase, wctx, kWaitKvFull)) return false;
+        ++ring;
+        tc_fence_after();
+        const uint32_t v_smem = smem_ring + slot * kSlotBytes;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          umma_ts(tmem_base + kTmemO, tmem_base + buffer * 128 + 64 + (4 * half + kk) * 8,
+                  umma_smem_desc(v_smem + kk * 2048, kVPanel, 1024), idesc_pv, accumulate || kk > 0);
+        }
+        tc_commit(bar_kv_empty + 8 * slot);
+        return true;
+      };
       for (int tile; ok && (tile = tiles.pop_thread(popped, wctx)) >= 0;) {
         FwdTile t = decode_tile(p, tile / kSplit, kBlockM);
-        const int dh = tile % kSplit;
         if (!t.valid) continue;
         const int n_blocks = count_blocks(t);
         if (n_blocks == 0) continue;
         const uint32_t q_phase = q_count & 1;
         ++q_count;
         if (!mbar_wait(bar_q_full, q_phase, wctx, kWaitQFull)) { ok = false; break; }
-        // The S buffers alternate with the block index of the work item; their barrier phases count per buffer.
         for (int i = 0; ok && i < imin(2, n_blocks); ++i) ok = issue_s(i);
         for (int n = 0; ok && n < n_blocks; ++n) {
           const int buffer = n & 1;
-          const uint32_t v_index = ring++;
-          if (!wait_kv(v_index)) { ok = false; break; }
-          // phase of p_full[buffer]: number of earlier blocks that used this buffer
+          // keys [64,128) first: their probabilities are stored first
+          if (!mbar_wait(bar_p_half + 8 * buffer, p_phase[buffer], wctx, kWaitPFull)) { ok = false; break; }
+          trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 300 + (n % 100));  // first half of P present
+          if (!issue_pv_half(buffer, 1, n > 0)) { ok = false; break; }
+          trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 400 + (n % 100));  // PV of the first half issued
           if (!mbar_wait(bar_p_full + 8 * buffer, p_phase[buffer], wctx, kWaitPFull)) { ok = false; break; }
+          trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 500 + (n % 100));  // all of P present
           p_phase[buffer] ^= 1;
-          tc_fence_after();
-          const uint32_t v_smem = smem_kv + (v_index % NS) * kKvBytes;
-#pragma unroll
-          for (int kk = 0; kk < kSubN / 16; ++kk) {
-            umma_ts(tmem_base + kTmemO, tmem_base + buffer * 128 + 64 + kk * 8,
-                    umma_smem_desc(v_smem + kk * 2048, kKvPanel, 1024), idesc_pv, n > 0 || kk > 0);
-          }
+          if (!issue_pv_half(buffer, 0, true)) { ok = false; break; }
           tc_commit(bar_pv_done);
-          tc_commit(bar_kv_empty + 8 * (v_index % NS));
-          ++blocks;
+          trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 600 + (n % 100));  // PV of the second half issued
           if (n + 2 < n_blocks) ok = issue_s(buffer);
         }
         if (ok) tc_commit(bar_q_empty);
@@ -244,18 +230,17 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     const uint32_t t_o = tmem_base + lane_addr + kTmemO;
     const float scale_log2 = p.scale_log2;
-    uint32_t blocks = 0;
+    uint32_t blocks = 0, popped = 0;
     uint32_t s_phase[2] = {0, 0};
     bool ok = true;
-    uint32_t popped = 0;
     for (int tile; ok && (tile = tiles.pop_warp(popped, wctx)) >= 0;) {
       FwdTile t = decode_tile(p, tile / kSplit, kBlockM);
       const int dh = tile % kSplit;
       if (!t.valid) continue;
       const int row = t.m0 + row_in_tile;
-      SubBlockCursor cur;
+      KeyCursorT<kBits> cur;
       cur.init(&pr, t.seq, t.s, t.m0, imin(t.m0 + kBlockM, t.s.lq));
-      const int band_lo = cur.cursor.band.lo(row), band_hi = cur.cursor.band.hi(row);
+      const int band_lo = cur.band.lo(row), band_hi = cur.band.hi(row);
       float m = -INFINITY, l = 0.f;
       TopApart top;  // keys set aside for the log-sum-exp of rows with a near-zero maximum (fwd_common.cuh)
       int tile_blocks = 0;
@@ -266,10 +251,8 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (!mbar_wait_warp(bar_s_full + 8 * buffer, s_phase[buffer], wctx, kWaitSFull)) { ok = false; break; }
         s_phase[buffer] ^= 1;
         tc_fence_after();
-        float2 s[32];  // 64 scores
-        tmem_ld32(t_s, reinterpret_cast<uint32_t*>(s));
-        tmem_ld32(t_s + 32, reinterpret_cast<uint32_t*>(s) + 32);
-        tc_wait_ld();
+        const bool traced = blockIdx.x == 0 && threadIdx.x == 0 && popped == 1;
+        trace_event(wctx, traced, 1, trace_n, 2000 + (tile_blocks % 100));  // scores present
         int lo, hi;
         if (kb.banded) {
           lo = band_lo - kb.col0;
@@ -278,28 +261,48 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           lo = 0;
           hi = kb.limit - kb.col0;
         }
-        const bool masked_block = __any_sync(0xffffffffu, lo > 0 || hi < kSubN);
-        if (masked_block) {
+        const bool masked = __any_sync(0xffffffffu, lo > 0 || hi < kBlockN);
+        auto apply_mask = [&](float2* values, int first_column) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            s[i].x = (2 * i >= lo && 2 * i < hi) ? s[i].x : -INFINITY;
-            s[i].y = (2 * i + 1 >= lo && 2 * i + 1 < hi) ? s[i].y : -INFINITY;
+            const int c = first_column + 2 * i;
+            values[i].x = (c >= lo && c < hi) ? values[i].x : -INFINITY;
+            values[i].y = (c + 1 >= lo && c + 1 < hi) ? values[i].y : -INFINITY;
           }
-        }
-        float bm0 = fmaxf(s[0].x, s[0].y), bm1 = fmaxf(s[1].x, s[1].y);
-        float bm2 = fmaxf(s[2].x, s[2].y), bm3 = fmaxf(s[3].x, s[3].y);
+        };
+        auto max_of = [&](const float2* values) {
+          float a = fmaxf(values[0].x, values[0].y), b = fmaxf(values[1].x, values[1].y);
+          float c = fmaxf(values[2].x, values[2].y), d = fmaxf(values[3].x, values[3].y);
 #pragma unroll
-        for (int i = 4; i < 32; i += 4) {
-          bm0 = fmaxf(bm0, fmaxf(s[i].x, s[i].y));
-          bm1 = fmaxf(bm1, fmaxf(s[i + 1].x, s[i + 1].y));
-          bm2 = fmaxf(bm2, fmaxf(s[i + 2].x, s[i + 2].y));
-          bm3 = fmaxf(bm3, fmaxf(s[i + 3].x, s[i + 3].y));
-        }
-        const float part_a = fmaxf(bm0, bm2), part_b = fmaxf(bm1, bm3);  // even and odd pairs of columns
-        const float block_max = fmaxf(part_a, part_b);
+          for (int i = 4; i < 32; i += 4) {
+            a = fmaxf(a, fmaxf(values[i].x, values[i].y));
+            b = fmaxf(b, fmaxf(values[i + 1].x, values[i + 1].y));
+            c = fmaxf(c, fmaxf(values[i + 2].x, values[i + 2].y));
+            d = fmaxf(d, fmaxf(values[i + 3].x, values[i + 3].y));
+          }
+          return make_float2(fmaxf(a, c), fmaxf(b, d));  // maxima over the even and over the odd pairs of columns
+        };
+        // Pass 1: row maximum. Columns [0,64) are read for the maximum only and read again in pass 2; columns
+        // [64,128) stay in registers, because P goes over them.
+        float2 low[32], high[32];
+        tmem_ld32(t_s, reinterpret_cast<uint32_t*>(low));
+        tmem_ld32(t_s + 32, reinterpret_cast<uint32_t*>(low) + 32);
+        tc_wait_ld();
+        if (masked) apply_mask(low, 0);
+        const float2 max_low = max_of(low);
+        tmem_ld32(t_s + 64, reinterpret_cast<uint32_t*>(high));
+        tmem_ld32(t_s + 96, reinterpret_cast<uint32_t*>(high) + 32);
+        tc_wait_ld();
+        if (masked) apply_mask(high, 64);
+        const float2 max_high = max_of(high);
+        // Maxima over two interleaved halves of the block (even and odd pairs of columns): under a causal or window mask
+        // both halves hold visible keys as soon as the row sees more than two keys of the block.
+        const float max_even = fmaxf(max_low.x, max_high.x), max_odd = fmaxf(max_low.y, max_high.y);
+        const float block_max = fmaxf(max_even, max_odd);
         const float m_new = fmaxf(m, block_max);
-        const bool set_apart = sets_keys_apart(top, part_a, part_b, scale_log2);
+        const bool set_apart = sets_keys_apart(top, max_even, max_odd, scale_log2);
         const bool counting = __any_sync(0xffffffffu, set_apart);
+        trace_event(wctx, traced, 1, trace_n, 2100 + (tile_blocks % 100));  // row maximum known
         const bool grow = (m_new - m) * scale_log2 > 8.f;  // also true when m is -inf and m_new is finite
         if (__any_sync(0xffffffffu, grow)) {
           float alpha = 1.f;
@@ -327,30 +330,46 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const float2 scale2 = make_float2(scale_log2, scale_log2), shift2 = make_float2(-mc, -mc);
         float sum_counted = 0.f;
         if (counting)  // rare: the block sum without the keys set aside, from the scores still in TMEM
-          sum_counted = sum_without_keys_apart<kSubN>(top, l, set_apart, block_max, t_s, masked_block, lo, hi, scale_log2, mc);
+          sum_counted = sum_without_keys_apart<kBlockN>(top, l, set_apart, block_max, t_s, masked, lo, hi, scale_log2, mc);
         float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
+        // 64 scores -> 64 probabilities (BF16) stored at P columns [first_p_column, first_p_column + 32)
+        auto exponentiate = [&](const float2* values, uint32_t first_p_column) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t packed[16];
+          for (int c = 0; c < 2; ++c) {
+            uint32_t packed[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float2 x = __ffma2_rn(s[16 * c + i], scale2, shift2);
-            float2 e;
-            e.x = ex2_approx(x.x);
-            e.y = ex2_approx(x.y);
-            if (i & 1) sum_b = __fadd2_rn(sum_b, e); else sum_a = __fadd2_rn(sum_a, e);
-            packed[i] = pack_bf16x2(e.x, e.y);
+            for (int i = 0; i < 16; ++i) {
+              const float2 x = __ffma2_rn(values[16 * c + i], scale2, shift2);
+              float2 e;
+              e.x = ex2_approx(x.x);
+              e.y = ex2_approx(x.y);
+              if (i & 1) sum_b = __fadd2_rn(sum_b, e); else sum_a = __fadd2_rn(sum_a, e);
+              packed[i] = pack_bf16x2(e.x, e.y);
+            }
+            tmem_st16(t_s + 64 + first_p_column + 16 * c, packed);
           }
-          tmem_st16(t_s + 64 + 16 * c, packed);
-        }
+        };
+        // Pass 2 for columns [0,64): the loads are in flight while the upper half is exponentiated.
+        tmem_ld32(t_s, reinterpret_cast<uint32_t*>(low));
+        tmem_ld32(t_s + 32, reinterpret_cast<uint32_t*>(low) + 32);
+        exponentiate(high, 32);
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_p_half + 8 * buffer);  // keys [64,128): their half of the PV product may start
+        trace_event(wctx, traced, 1, trace_n, 2200 + (tile_blocks % 100));  // first half of P stored
+        tc_wait_ld();
+        if (masked) apply_mask(low, 0);
+        exponentiate(low, 0);
         l += counting ? sum_counted : (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
-        // Observe the PV product of the previous block before releasing this one. The scores of block n only prove
-        // that PV(n - 2) has completed, so without this wait the barrier could be two completions away from the one
-        // the epilogue waits for, which a parity wait cannot tell apart from "done".
+        trace_event(wctx, traced, 1, trace_n, 2300 + (tile_blocks % 100));  // second half exponentiated
+        // Observe the PV product of the previous block before releasing this one: the scores of block n only prove that
+        // PV(n - 2) has completed, and a parity wait cannot tell a barrier that is two completions behind from one that
+        // is done.
         if (tile_blocks > 0 && !mbar_wait_warp(bar_pv_done, (blocks - 1) & 1, wctx, kWaitPvDone)) { ok = false; break; }
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar_p_full + 8 * buffer);
+        trace_event(wctx, traced, 1, trace_n, 2400 + (tile_blocks % 100));  // all of P stored
         ++blocks;
         ++tile_blocks;
       }
@@ -391,7 +410,7 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
         }
       }
-      if (row_valid && dh == 0) *lse_ptr = lse_row;  // both halves hold the same statistics
+      if (row_valid && dh == 0) *lse_ptr = lse_row;
       tc_fence_before();
     }
   }
@@ -406,27 +425,30 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (warp == 4) tmem_dealloc(tmem_base, 512);
 }
 
-template <int kSplit>
-static int launch_fwd_wide(const b200fa_fwd_args& a, cudaStream_t stream) {
-  using Cfg = wide::Config<kSplit>;
+int launch_fwd_512(const b200fa_fwd_args& a, cudaStream_t stream) {
   FwdParams p;
   CUtensorMap map_q, map_k, map_v;
   bool nothing_to_do = false;
-  int status = prepare_forward(a, stream, wide::D * kSplit, kBlockM, wide::kSubN, &p, &map_q, &map_k, &map_v, &nothing_to_do);
+  int status = prepare_forward(a, stream, d512::D * d512::kSplit, kBlockM, kBlockN, &p, &map_q, &map_k, &map_v, &nothing_to_do, 64);
   if (status != B200FA_OK || nothing_to_do) return status;
-  static bool attribute_set[64] = {false};
-  status = set_dynamic_smem_once(reinterpret_cast<const void*>(&fwd_wide_kernel<kSplit>), Cfg::kSmemBytes, attribute_set);
-  if (status != B200FA_OK) return status;
   int sms = 0;
   status = device_sm_count(&sms);
   if (status != B200FA_OK) return status;
-  const int tiles = p.num_tiles * kSplit;
+  const int tiles = p.num_tiles * d512::kSplit;
   const int grid = tiles < sms ? tiles : sms;
-  fwd_wide_kernel<kSplit><<<grid, wide::kThreads, Cfg::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+  if (a.problem.visibility_bits) {
+    static bool attribute_set[64] = {false};
+    status = set_dynamic_smem_once(reinterpret_cast<const void*>(&fwd_d512_kernel<true>), d512::kSmemBytes, attribute_set);
+    if (status != B200FA_OK) return status;
+    fwd_d512_kernel<true><<<grid, d512::kThreads, d512::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+  } else {
+    static bool attribute_set[64] = {false};
+    status = set_dynamic_smem_once(reinterpret_cast<const void*>(&fwd_d512_kernel<false>), d512::kSmemBytes, attribute_set);
+    if (status != B200FA_OK) return status;
+    fwd_d512_kernel<false><<<grid, d512::kThreads, d512::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+  }
   B200FA_CUDA_CHECK(cudaGetLastError());
   return B200FA_OK;
 }
-
-int launch_fwd_512(const b200fa_fwd_args& a, cudaStream_t stream) { return launch_fwd_wide<2>(a, stream); }
 
 }  // namespace b200fa
