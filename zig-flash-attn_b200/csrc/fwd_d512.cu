@@ -166,7 +166,9 @@ fwd_d512_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       auto issue_s = [&](int buffer) -> bool {
         for (int part = 0; part < kParts; ++part) {
           const uint32_t slot = ring % NS, phase = (ring / NS) & 1;
+          trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 100 + part);  // waiting for a K part
           if (!mbar_wait(bar_kv_full + 8 * slot, phase, wctx, kWaitKvFull)) return false;
+          trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 110 + part);  // K part present
           ++ring;
           tc_fence_after();
           const uint32_t k_smem = smem_ring + slot * kSlotBytes;
@@ -179,12 +181,15 @@ fwd_d512_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           tc_commit(bar_kv_empty + 8 * slot);
         }
         tc_commit(bar_s_full + 8 * buffer);
+        trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 120);  // scores issued
         return true;
       };
       // O += P[:, 64 h .. 64 h + 64) V_half: the next slot of the ring holds those 64 keys.
       auto issue_pv_half = [&](int buffer, int half, bool accumulate) -> bool {
         const uint32_t slot = ring % NS, phase = (ring / NS) & 1;
+        trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 130 + half);  // waiting for a V half
         if (!mbar_wait(bar_kv_full + 8 * slot, phase, wctx, kWaitKvFull)) return false;
+        trace_event(wctx, blockIdx.x == 0 && q_count == 1, 0, trace_n, 140 + half);  // V half present
         ++ring;
         tc_fence_after();
         const uint32_t v_smem = smem_ring + slot * kSlotBytes;
