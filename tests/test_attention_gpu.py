@@ -78,6 +78,32 @@ def test_packed_query_heads_equal_the_unpacked_instance_bit_for_bit():
         assert torch.equal(out, out_wide) and torch.equal(lse, lse_wide), (heads_q, heads_kv, d, window)
 
 
+def test_packed_query_heads_in_packed_batches_equal_the_unpacked_instance_bit_for_bit():
+    """The same for packed (varlen) batches, whose work list then has entries of 256 / group tokens: sequences of every
+    length class, empty ones, more keys than queries and the reverse, causal masks and windows. `out` is equal bit for
+    bit. The log-sum-exp may differ in its last bit: when a row of a warp sets keys aside (a near-zero block maximum,
+    fwd_common.cuh), every row of that warp sums the block in the order of that rare path, so the rounding of a row's
+    sum depends on which rows share its warp."""
+    cases = [([300, 0, 1, 513, 128, 77], [300, 5, 1, 600, 100, 77], 8, 2, 128, (-1, 0)),
+             ([1024, 31, 257], [1024, 64, 300], 16, 1, 64, (100, 0)),
+             ([200, 333], [450, 333], 128, 1, 128, (-1, -1)),
+             ([513, 2, 700, 64], [513, 2, 650, 90], 4, 2, 96, (-1, 17))]
+    for lengths_q, lengths_k, heads_q, heads_kv, d, window in cases:
+        torch.manual_seed(sum(lengths_q) + heads_q)
+        cu_q = torch.nn.functional.pad(torch.tensor(lengths_q).cumsum(0), (1, 0)).int().cuda()
+        cu_k = torch.nn.functional.pad(torch.tensor(lengths_k).cumsum(0), (1, 0)).int().cuda()
+        q, k, v = randn(sum(lengths_q), heads_q, d), randn(sum(lengths_k), heads_kv, d), randn(sum(lengths_k), heads_kv, d)
+        group = heads_q // heads_kv
+        options = dict(window_size=window, return_attn_probs=True)
+        out, lse = zigfa.flash_attn_varlen_func(q, k, v, cu_q, cu_k, max(lengths_q), max(lengths_k), **options)
+        wide_k, wide_v = k.repeat_interleave(group, dim=1), v.repeat_interleave(group, dim=1)
+        out_wide, lse_wide = zigfa.flash_attn_varlen_func(q, wide_k, wide_v, cu_q, cu_k, max(lengths_q), max(lengths_k), **options)
+        assert torch.equal(out, out_wide), (heads_q, heads_kv, d, window)
+        finite = torch.isfinite(lse_wide)
+        assert torch.equal(torch.isfinite(lse), finite), (heads_q, heads_kv, d, window)
+        assert ((lse - lse_wide)[finite].abs() <= 2.0**-22 * lse_wide[finite].abs().clamp(min=1.0)).all(), (heads_q, heads_kv, d, window)
+
+
 def test_large_gqa_groups_and_long_sequences():
     for batch, heads_q, heads_kv, seqlen in [(3, 18, 6, 4096), (8, 16, 2, 2048), (1, 8, 2, 4096), (1, 32, 1, 1024)]:
         torch.manual_seed(seqlen + heads_q)

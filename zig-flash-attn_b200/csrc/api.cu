@@ -182,8 +182,8 @@ int b200fa_device_status(void) {
 
 size_t b200fa_fwd_workspace_bytes(const b200fa_problem* p) {
   if (!p->cu_seqlens_q) return fwd_split_workspace_bytes(*p);  // partial results of the split-KV path, usually 0
-  // work items are 256 query rows, 128 for head_dim 256
-  const int tile_rows = p->head_dim >= 256 ? kBlockM : kFwdTileM;
+  // work-list entries cover 256 query rows, 128 at head_dim 256 and 512, 256 >> shift tokens where query heads are packed
+  const int tile_rows = p->head_dim >= 256 ? kBlockM : kFwdTileM >> fwd_pack_shift(*p);
   return static_cast<size_t>(work_list_entries(p->seqlen_q, p->batch, tile_rows)) * 8;
 }
 

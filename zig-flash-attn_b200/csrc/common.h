@@ -50,6 +50,8 @@ int device_sm_count(int* count);
 // Bytes of partial results the split-KV forward path wants for this problem (0 = the problem is not split). Defined in
 // fwd.cu; a pure function of the shapes.
 size_t fwd_split_workspace_bytes(const b200fa_problem& problem);
+// log2 of the query heads that the forward kernel packs into the rows of a work item for this problem (fwd.cu).
+int fwd_pack_shift(const b200fa_problem& problem);
 // Raises the dynamic shared-memory limit of `kernel` once per device (function attributes are per device; `done` is
 // the caller's per-kernel record, indexed by device ordinal).
 int set_dynamic_smem_once(const void* kernel, int bytes, bool (&done)[64]);

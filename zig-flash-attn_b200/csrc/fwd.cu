@@ -636,23 +636,31 @@ int acquire_tile_counter(cudaStream_t stream, int** counter) {
 // The plan is a pure function of the shapes (it assumes the 148 SMs of a B200), so the workspace size it implies can be
 // computed without a device.
 constexpr int kPlanSms = 148;
+// Entries of the work list that b200fa_fwd_noalloc keeps in device memory: (sequence, block) pairs; one entry covers 256
+// query rows (128 at head_dim 256 and 512; 256 >> shift tokens of every head of a group when query heads are packed).
+constexpr int kStaticWorkListEntries = 8192;
 
-// log2 of the query heads packed into the rows of a work item of fwd_kernel (0 = no packing): fixed-length problems
-// whose query heads per key head are a power of two between 2 and 128. B200FA_PACK_GQA=0 in the environment turns it off
-// (tuning comparisons). A pure function of the shapes, like the split plan that builds on it.
+// log2 of the query heads packed into the rows of a work item of fwd_kernel (0 = no packing): problems without
+// visibility bits whose query heads per key head are a power of two between 2 and 128. B200FA_PACK_GQA=0 in the
+// environment turns it off (tuning comparisons). A pure function of the shapes, like the split plan and the work-list
+// size that build on it. A packed (varlen) batch keeps unpacked work items when its work list at the finer granularity
+// (256 >> shift tokens per entry) would not fit the built-in scratch of b200fa_fwd_noalloc, so that entry point serves
+// the same batches as before.
 static int pack_shift_of(const b200fa_problem& bp) {
   static const bool disabled = [] {
     const char* value = getenv("B200FA_PACK_GQA");
     return value && value[0] == '0';
   }();
-  if (disabled || bp.cu_seqlens_q || bp.visibility_bits || bp.head_dim > 128 || bp.heads_kv <= 0) return 0;
+  if (disabled || bp.visibility_bits || bp.head_dim > 128 || bp.heads_kv <= 0) return 0;
   if (bp.heads_q % bp.heads_kv) return 0;
   const int group = bp.heads_q / bp.heads_kv;
   if (group < 2 || group > kBlockM || (group & (group - 1))) return 0;
   int shift = 0;
   while ((1 << shift) < group) ++shift;
+  if (bp.cu_seqlens_q && work_list_entries(bp.seqlen_q, bp.batch, kFwdTileM >> shift) > kStaticWorkListEntries) return 0;
   return shift;
 }
+int fwd_pack_shift(const b200fa_problem& bp) { return pack_shift_of(bp); }
 
 struct SplitPlan {
   int splits;
@@ -758,7 +766,7 @@ int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim,
   p.o_partial = nullptr;
   p.lse_partial = nullptr;
   p.partial_rows = 0;
-  p.pack_shift = packed ? 0 : pack_shift;
+  p.pack_shift = pack_shift;
   p.tile_counter = nullptr;
   p.m_blocks = 0;
   p.head_dim = bp.head_dim;
@@ -769,16 +777,17 @@ int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim,
   const int64_t rows_q = bp.seqlen_q, rows_k = bp.seqlen_k;
   const int64_t tensor_batch = packed ? 1 : bp.batch;
   if (packed) {
-    const int64_t entries = work_list_entries(rows_q, bp.batch, tile_rows);
+    const int entry_rows = tile_rows >> p.pack_shift;  // tokens per work-list entry
+    const int64_t entries = work_list_entries(rows_q, bp.batch, entry_rows);
     B200FA_REQUIRE(a.workspace_bytes >= b200fa_fwd_workspace_bytes(&bp) && (entries == 0 || a.workspace),
                    "forward workspace is too small: need %zu bytes", b200fa_fwd_workspace_bytes(&bp));
     if (entries == 0) return B200FA_OK;
     const int32_t* other = bp.cu_visible_k ? bp.cu_visible_k : bp.cu_seqlens_k;
-    int status = b200fa_work_list(bp.cu_seqlens_q, other, bp.batch, tile_rows, 1, (int32_t)entries,
+    int status = b200fa_work_list(bp.cu_seqlens_q, other, bp.batch, entry_rows, 1, (int32_t)entries,
                                   static_cast<int32_t*>(a.workspace), stream);
     if (status != B200FA_OK) return status;
     p.work_list = static_cast<const int2*>(a.workspace);
-    p.num_tiles = (int)(entries * bp.heads_q);
+    p.num_tiles = (int)(entries * (bp.heads_q >> p.pack_shift));
   } else {
     p.m_blocks = ceil_div(bp.seqlen_q, tile_rows >> p.pack_shift);
     p.num_tiles = p.m_blocks * bp.batch * (bp.heads_q >> p.pack_shift);
@@ -789,7 +798,7 @@ int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim,
     p.div_per_group = FastDiv::make((uint32_t)(p.m_blocks * group));
     p.div_group = FastDiv::make((uint32_t)group);
     p.div_heads_kv = FastDiv::make((uint32_t)bp.heads_kv);
-    p.div_heads_q = FastDiv::make((uint32_t)bp.heads_q);
+    p.div_heads_q = FastDiv::make((uint32_t)(bp.heads_q >> p.pack_shift));  // work items per work-list entry
     p.div_ratio = FastDiv::make((uint32_t)p.ratio);
   }
   if (p.num_tiles <= 0 || rows_q == 0) return B200FA_OK;
@@ -904,7 +913,6 @@ int launch_fwd(const b200fa_fwd_args& a, cudaStream_t stream) {
 // the work list of a packed (varlen / inter-sequence) batch; here it lives in a fixed array in device memory that
 // belongs to the library. Every GPU that loads the library holds these 64 KiB until the process exits.
 namespace b200fa {
-constexpr int kStaticWorkListEntries = 8192;  // (sequence, block) pairs; one entry covers 256 query rows (128 at head_dim 256 and 512)
 static __device__ __align__(256) int32_t g_static_work_list[2 * kStaticWorkListEntries];
 
 // Device address of the array on the current device. `g_static_work_list` as written in host code is only a host-side

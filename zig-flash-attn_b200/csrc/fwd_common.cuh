@@ -225,11 +225,11 @@ __device__ __forceinline__ FwdTile decode_tile(const FwdParams& p, int tile, int
   FwdTile t;
   const Problem& pr = p.prob;
   if (p.work_list) {
-    int entry = p.div_heads_q.div(tile);
-    t.head = tile - entry * pr.heads_q;
+    int entry = p.div_heads_q.div(tile);  // work items per entry: query heads, or key heads when groups are packed
+    t.head = (tile - entry * (pr.heads_q >> p.pack_shift)) << p.pack_shift;  // packed: the first head of the group
     int2 e = p.work_list[entry];
     t.seq = e.x;
-    t.m0 = e.y * tile_rows;
+    t.m0 = e.y * (tile_rows >> p.pack_shift);
     t.valid = e.x < pr.batch;
   } else {
     // Work items that run at the same time share K and V: all query blocks and query heads of one (batch entry, key
