@@ -62,9 +62,8 @@ def test_workspace_sizes_are_shape_functions():
     # groups of four query heads are packed into the rows of a work item: an entry covers 64 tokens of all four heads
     grouped = problem(batch=3, seqlen_q=1000, seqlen_k=900, cu_seqlens_q=8, cu_seqlens_k=8)
     assert library.b200fa_fwd_workspace_bytes(ctypes.byref(grouped)) == library.b200fa_work_list_entries(1000, 3, 64) * 8
-    # ... unless the finer work list would not fit the scratch of b200fa_fwd_noalloc (8192 entries)
     long_batch = problem(batch=3, seqlen_q=1_000_000, seqlen_k=900, cu_seqlens_q=8, cu_seqlens_k=8)
-    assert library.b200fa_fwd_workspace_bytes(ctypes.byref(long_batch)) == library.b200fa_work_list_entries(1_000_000, 3, 256) * 8
+    assert library.b200fa_fwd_workspace_bytes(ctypes.byref(long_batch)) == library.b200fa_work_list_entries(1_000_000, 3, 64) * 8
     # groups that are no power of two and head dims above 128 keep one head per work item
     odd_group = problem(batch=3, seqlen_q=1000, seqlen_k=900, heads_q=6, heads_kv=2, cu_seqlens_q=8, cu_seqlens_k=8)
     assert library.b200fa_fwd_workspace_bytes(ctypes.byref(odd_group)) == entries * 8

@@ -51,7 +51,7 @@ def prepared_visibility(cu, visible):
     return dict(visibility_bits=bits, visibility_bits_t=bits_t, cu_visible_k=cu_visible_k, cu_visible_q=cu_visible_q)
 
 
-def run_both(lengths, heads_q, heads_kv, head_dim, window, seed, visible=None):
+def run_both(lengths, heads_q, heads_kv, head_dim, window, seed, visible=None, same_work_list=True):
     library = lib.library()
     stream = torch.cuda.current_stream().cuda_stream
     torch.manual_seed(seed)
@@ -69,9 +69,22 @@ def run_both(lengths, heads_q, heads_kv, head_dim, window, seed, visible=None):
     assert library.b200fa_fwd_noalloc(ctypes.byref(bare), stream) == 0, lib.last_error()
     torch.cuda.synchronize()
     assert not torch.isnan(out_regular).any()
-    # same kernels, same work list: the results are identical, not merely close
-    assert torch.equal(out_bare, out_regular)
-    assert torch.equal(lse_bare, lse_regular)
+    if same_work_list:
+        # same kernels, same work list: the results are identical, not merely close
+        assert torch.equal(out_bare, out_regular)
+        assert torch.equal(lse_bare, lse_regular)
+    else:
+        # Other rows share a row's warp. When one of them sets keys aside (a near-zero block maximum, fwd_common.cuh) the
+        # whole warp sums the block in the order of that rare path, so a row's sum may round differently in its last
+        # bit: the log-sum-exp moves by one FP32 step, and 1 / sum may tip the BF16 rounding of an output element (one
+        # element in 138 million in this batch).
+        different = out_bare != out_regular
+        assert int(different.sum()) <= max(1, out_regular.numel() // 10_000_000)
+        step = (out_bare.float() - out_regular.float()).abs()
+        assert (step <= 2.0**-7 * out_regular.float().abs()).all()
+        finite = torch.isfinite(lse_regular)
+        assert torch.equal(torch.isfinite(lse_bare), finite)
+        assert ((lse_bare - lse_regular)[finite].abs() <= 2.0**-22 * lse_regular[finite].abs().clamp(min=1.0)).all()
 
 
 def test_noalloc_forward_matches_the_regular_entry_point_twice_in_a_row():
@@ -92,6 +105,19 @@ def test_noalloc_forward_with_an_inter_sequence_batch():
     visible = [[j == i or j == prefix_of[i] for j in range(len(lengths))] for i in range(len(lengths))]
     run_both(lengths, 8, 2, 128, (-1, 0), seed=15, visible=visible)
     run_both(lengths[:3], 4, 4, 256, (-1, 0), seed=16, visible=[row[:3] for row in visible[:3]])
+
+
+def test_noalloc_forward_runs_unpacked_when_the_finer_work_list_does_not_fit():
+    """Groups of four query heads are packed into work items of 64 tokens, whose work list (11 390 entries here) exceeds
+    the built-in scratch; the list with one head per work item (5097 entries) fits, so the call runs that way and returns
+    what the regular entry point computes with packed heads."""
+    library = lib.library()
+    lengths = [180] * 3000
+    probe = lib.Problem(batch=len(lengths), seqlen_q=sum(lengths), seqlen_k=sum(lengths), heads_q=4, heads_kv=1, head_dim=64,
+                        window_left=-1, window_right=0, softmax_scale=0.125, cu_seqlens_q=8, cu_seqlens_k=8)
+    assert library.b200fa_fwd_workspace_bytes(ctypes.byref(probe)) > 8192 * 8
+    assert library.b200fa_work_list_entries(sum(lengths), len(lengths), 256) <= 8192
+    run_both(lengths, 4, 1, 64, (-1, 0), seed=17, same_work_list=False)
 
 
 def test_noalloc_forward_refuses_batches_beyond_its_scratch():

@@ -643,9 +643,9 @@ constexpr int kStaticWorkListEntries = 8192;
 // log2 of the query heads packed into the rows of a work item of fwd_kernel (0 = no packing): problems without
 // visibility bits whose query heads per key head are a power of two between 2 and 128. B200FA_PACK_GQA=0 in the
 // environment turns it off (tuning comparisons). A pure function of the shapes, like the split plan and the work-list
-// size that build on it. A packed (varlen) batch keeps unpacked work items when its work list at the finer granularity
-// (256 >> shift tokens per entry) would not fit the built-in scratch of b200fa_fwd_noalloc, so that entry point serves
-// the same batches as before.
+// size that build on it. The work list of a packed (varlen) batch then has entries of 256 >> shift tokens; a call whose
+// workspace holds only the coarser list (the built-in scratch of b200fa_fwd_noalloc for a large batch) runs with one
+// head per work item instead (prepare_forward).
 static int pack_shift_of(const b200fa_problem& bp) {
   static const bool disabled = [] {
     const char* value = getenv("B200FA_PACK_GQA");
@@ -657,7 +657,6 @@ static int pack_shift_of(const b200fa_problem& bp) {
   if (group < 2 || group > kBlockM || (group & (group - 1))) return 0;
   int shift = 0;
   while ((1 << shift) < group) ++shift;
-  if (bp.cu_seqlens_q && work_list_entries(bp.seqlen_q, bp.batch, kFwdTileM >> shift) > kStaticWorkListEntries) return 0;
   return shift;
 }
 int fwd_pack_shift(const b200fa_problem& bp) { return pack_shift_of(bp); }
@@ -777,10 +776,17 @@ int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim,
   const int64_t rows_q = bp.seqlen_q, rows_k = bp.seqlen_k;
   const int64_t tensor_batch = packed ? 1 : bp.batch;
   if (packed) {
+    int64_t entries = work_list_entries(rows_q, bp.batch, tile_rows >> p.pack_shift);
+    if (p.pack_shift > 0 && a.workspace_bytes < static_cast<size_t>(entries) * 8) {
+      // The finer work list of packed query heads does not fit what the caller has: one head per work item (same
+      // results; b200fa_fwd_workspace_bytes asks for the finer list).
+      p.pack_shift = 0;
+      entries = work_list_entries(rows_q, bp.batch, tile_rows);
+    }
     const int entry_rows = tile_rows >> p.pack_shift;  // tokens per work-list entry
-    const int64_t entries = work_list_entries(rows_q, bp.batch, entry_rows);
-    B200FA_REQUIRE(a.workspace_bytes >= b200fa_fwd_workspace_bytes(&bp) && (entries == 0 || a.workspace),
-                   "forward workspace is too small: need %zu bytes", b200fa_fwd_workspace_bytes(&bp));
+    B200FA_REQUIRE(a.workspace_bytes >= static_cast<size_t>(entries) * 8 && (entries == 0 || a.workspace),
+                   "forward workspace is too small: need %zu bytes (%zu recommended)", static_cast<size_t>(entries) * 8,
+                   b200fa_fwd_workspace_bytes(&bp));
     if (entries == 0) return B200FA_OK;
     const int32_t* other = bp.cu_visible_k ? bp.cu_visible_k : bp.cu_seqlens_k;
     int status = b200fa_work_list(bp.cu_seqlens_q, other, bp.batch, entry_rows, 1, (int32_t)entries,
@@ -940,8 +946,11 @@ extern "C" int b200fa_fwd_noalloc(const b200fa_fwd_args* args, void* stream) {
   B200FA_REQUIRE(problem.batch >= 0 && problem.seqlen_q >= 0 && problem.seqlen_k >= 0, "negative sizes");
   // Only the work list of a packed batch is scratch this entry point must provide; the partial results the split-KV path
   // of a fixed-length problem would like are optional (without room for them the problem runs unsplit).
-  const size_t needed = problem.cu_seqlens_q ? b200fa_fwd_workspace_bytes(&problem) : 0;
+  // (the list with one head per work item: where b200fa_fwd_workspace_bytes asks for the finer list of packed query
+  // heads and that does not fit, the batch runs unpacked)
   const int tile_rows = problem.head_dim >= 256 ? kBlockM : kFwdTileM;
+  const size_t needed =
+      problem.cu_seqlens_q ? static_cast<size_t>(work_list_entries(problem.seqlen_q, problem.batch, tile_rows)) * 8 : 0;
   B200FA_REQUIRE(needed <= sizeof(int32_t) * 2 * kStaticWorkListEntries,
                  "b200fa_fwd_noalloc: the batch needs a work list of %zu bytes (%zu entries of %d query rows at "
                  "head_dim %d) but the built-in scratch holds %zu bytes (%d entries); use b200fa_fwd with a "
