@@ -657,6 +657,8 @@ static int pack_shift_of(const b200fa_problem& bp) {
   if (group < 2 || group > kBlockM || (group & (group - 1))) return 0;
   int shift = 0;
   while ((1 << shift) < group) ++shift;
+  // The work list is written one sequence per thread: entries of fewer than 16 tokens would make that loop long.
+  if (bp.cu_seqlens_q && shift > 4) return 0;
   return shift;
 }
 int fwd_pack_shift(const b200fa_problem& bp) { return pack_shift_of(bp); }
