@@ -84,7 +84,7 @@ int b200fa_fwd(const b200fa_fwd_args* args, void* stream);
  * of a sequence at head_dim <= 128 ((total_q + 255 * batch) / 256 <= 8192) and 128 rows at head_dim 256 and 512
  * ((total_q + 127 * batch) / 128 <= 8192); larger batches are rejected with B200FA_ERR_INVALID and a
  * message. (Where the query heads of a group are packed into the rows of a work item -- a power-of-two number of query
- * heads per key head, at most 16 in a packed batch, head_dim <= 128, no visibility bits -- an entry covers 256 / group tokens and
+ * heads per key head, at most 16 in a packed batch, head_dim <= 128 -- an entry covers 256 / group tokens and
  * b200fa_fwd_workspace_bytes asks for that finer list; a call whose workspace holds only the list with one head per
  * work item, as this entry point's scratch may, runs unpacked (a row's sum of exponentials may then round differently
  * in its last bit; nothing else changes), so the limit above decides.) Fixed-length problems need no scratch and have no such limit. The call itself allocates and frees nothing.

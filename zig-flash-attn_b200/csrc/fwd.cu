@@ -640,8 +640,8 @@ constexpr int kPlanSms = 148;
 // query rows (128 at head_dim 256 and 512; 256 >> shift tokens of every head of a group when query heads are packed).
 constexpr int kStaticWorkListEntries = 8192;
 
-// log2 of the query heads packed into the rows of a work item of fwd_kernel (0 = no packing): problems without
-// visibility bits whose query heads per key head are a power of two between 2 and 128. B200FA_PACK_GQA=0 in the
+// log2 of the query heads packed into the rows of a work item of fwd_kernel (0 = no packing): problems whose query heads
+// per key head are a power of two between 2 and 128 (fixed-length, packed and inter-sequence batches alike). B200FA_PACK_GQA=0 in the
 // environment turns it off (tuning comparisons). A pure function of the shapes, like the split plan and the work-list
 // size that build on it. The work list of a packed (varlen) batch then has entries of 256 >> shift tokens; a call whose
 // workspace holds only the coarser list (the built-in scratch of b200fa_fwd_noalloc for a large batch) runs with one
@@ -651,7 +651,7 @@ static int pack_shift_of(const b200fa_problem& bp) {
     const char* value = getenv("B200FA_PACK_GQA");
     return value && value[0] == '0';
   }();
-  if (disabled || bp.visibility_bits || bp.head_dim > 128 || bp.heads_kv <= 0) return 0;
+  if (disabled || bp.head_dim > 128 || bp.heads_kv <= 0) return 0;
   if (bp.heads_q % bp.heads_kv) return 0;
   const int group = bp.heads_q / bp.heads_kv;
   if (group < 2 || group > kBlockM || (group & (group - 1))) return 0;
