@@ -566,6 +566,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                                          __uint_as_float(o[4 * i + 2]) * inv, __uint_as_float(o[4 * i + 3]) * inv);
             if (32 * c + 4 * i < p.head_dim) reinterpret_cast<float4*>(o_part)[8 * c + i] = v;
           }
+        } else if (row_valid && p.o_wide) {
+          // 32-byte stores: a lane writes whole sectors of its row (with 16-byte stores a warp instruction touches 32
+          // sectors and fills half of each)
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            uint32_t w[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              w[j] = pack_bf16x2(__uint_as_float(o[16 * i + 2 * j]) * inv, __uint_as_float(o[16 * i + 2 * j + 1]) * inv);
+            if (32 * c + 16 * i < p.head_dim) st_global_v8(o_row + 32 * c + 16 * i, w);
+          }
         } else if (row_valid) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -762,6 +773,9 @@ int prepare_forward(const b200fa_fwd_args& a, cudaStream_t stream, int head_dim,
   p.lse = a.softmax_lse;
   p.lse_batch_stride = packed ? 0 : a.lse_stride[0];
   p.lse_head_stride = a.lse_stride[1];
+  // every output row starts on a 32-byte boundary and holds a whole number of 32-byte pieces
+  p.o_wide = (reinterpret_cast<uintptr_t>(a.out) & 31) == 0 && (packed || a.out_stride[0] % 16 == 0) &&
+             a.out_stride[1] % 16 == 0 && a.out_stride[2] % 16 == 0 && bp.head_dim % 16 == 0;
   p.work_list = nullptr;
   p.splits = 1;
   p.o_partial = nullptr;

@@ -54,6 +54,7 @@ struct FwdParams {
   // of a work item are (token, head of the group) pairs, row = token << pack_shift | head, so a work item covers
   // 256 >> pack_shift tokens of all heads of one key head. 0: a work item is 256 tokens of one head.
   int pack_shift;
+  int o_wide;  // 1: the rows of the output may be written with 32-byte stores (alignment of base and strides)
 };
 
 // log2(1 + x) for 0 <= x < 1/16 from the series of ln(1 + x) up to x^6 (truncation error below 1e-9 relative).

@@ -403,7 +403,16 @@ fwd_d512_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         uint32_t o[32];
         tmem_ld32(t_o + 32 * c, o);
         tc_wait_ld();
-        if (row_valid) {
+        if (row_valid && p.o_wide) {  // 32-byte stores: a lane writes whole sectors of its row
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            uint32_t w[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              w[j] = pack_bf16x2(__uint_as_float(o[16 * i + 2 * j]) * inv, __uint_as_float(o[16 * i + 2 * j + 1]) * inv);
+            st_global_v8(o_row + 32 * c + 16 * i, w);
+          }
+        } else if (row_valid) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             uint4 v;

@@ -391,6 +391,12 @@ __device__ __forceinline__ float2 ex2_poly2(float2 x) {
   result.y = x.y > -127.f ? result.y : 0.f;
   return result;
 }
+// 32-byte store to global memory (the address must be 32-byte aligned).
+__device__ __forceinline__ void st_global_v8(void* address, const uint32_t* w) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(address), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+               "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t d;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
