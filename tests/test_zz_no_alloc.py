@@ -120,36 +120,6 @@ def test_noalloc_forward_runs_unpacked_when_the_finer_work_list_does_not_fit():
     run_both(lengths, 4, 1, 64, (-1, 0), seed=17, same_work_list=False)
 
 
-@pytest.mark.parametrize("head_dim", [64, 128, 256, 512])
-def test_output_on_a_16_byte_boundary_takes_the_narrow_stores(head_dim):
-    """The forward kernels write an output row with 32-byte stores when the tensor allows it (base address and strides
-    multiples of 32 bytes) and with 16-byte stores otherwise: the same problem written into a tensor that starts 16
-    bytes into its buffer gives the same bits."""
-    library = lib.library()
-    stream = torch.cuda.current_stream().cuda_stream
-    torch.manual_seed(head_dim)
-    lengths = [300, 129, 64]
-    total, heads_q, heads_kv = sum(lengths), 4, 2
-    q = torch.randn(total, heads_q, head_dim, device="cuda", dtype=torch.bfloat16)
-    k, v = (torch.randn(total, heads_kv, head_dim, device="cuda", dtype=torch.bfloat16) for _ in range(2))
-    cu = torch.tensor([0, *itertools.accumulate(lengths)], dtype=torch.int32, device="cuda")
-    problem = lib.make_problem(q, k, cu, cu, head_dim**-0.5, -1, 0)
-    workspace = torch.empty(max(library.b200fa_fwd_workspace_bytes(ctypes.byref(problem)), 1), dtype=torch.uint8, device="cuda")
-    aligned, out_aligned, lse_aligned = forward_arguments(q, k, v, cu, cu, (-1, 0), workspace)
-    assert out_aligned.data_ptr() % 32 == 0
-    assert library.b200fa_fwd(ctypes.byref(aligned), stream) == 0, lib.last_error()
-    shifted, _, lse_shifted = forward_arguments(q, k, v, cu, cu, (-1, 0), workspace)
-    buffer = torch.full((q.numel() + 8,), float("nan"), device="cuda", dtype=torch.bfloat16)
-    out_shifted = buffer[8:].view_as(q)
-    assert out_shifted.data_ptr() % 32 == 16
-    shifted.out = out_shifted.data_ptr()
-    assert library.b200fa_fwd(ctypes.byref(shifted), stream) == 0, lib.last_error()
-    torch.cuda.synchronize()
-    assert not torch.isnan(out_aligned).any()
-    assert torch.equal(out_shifted, out_aligned) and torch.equal(lse_shifted, lse_aligned)
-    assert torch.isnan(buffer[:8]).all()
-
-
 def test_noalloc_forward_refuses_batches_beyond_its_scratch():
     library = lib.library()
     # shape-only check on the host: 8193 sequences of one row need 8193 work-list entries, one more than the array holds

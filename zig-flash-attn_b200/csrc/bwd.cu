@@ -484,7 +484,16 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 #pragma unroll
             for (int i = 0; i < 32; ++i) acc[i] = 0;
           }
-          if (key_valid) {
+          if (key_valid && p.dkv_wide) {  // 32-byte stores: a lane writes whole sectors of its row
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              uint32_t w[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                w[j] = pack_bf16x2(__uint_as_float(acc[16 * i + 2 * j]) * mul, __uint_as_float(acc[16 * i + 2 * j + 1]) * mul);
+              if (32 * ch + 16 * i < p.head_dim) st_global_v8(dst + 4 * ch + 2 * i, w);
+            }
+          } else if (key_valid) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               uint4 v;
@@ -954,6 +963,10 @@ static int launch_bwd_d(const b200fa_bwd_args& a, cudaStream_t stream) {
   p.dv_batch_stride = packed ? 0 : a.dv_stride[0];
   p.dv_row_stride = a.dv_stride[1];
   p.dv_head_stride = a.dv_stride[2];
+  // every dK and dV row starts on a 32-byte boundary and holds a whole number of 32-byte pieces
+  p.dkv_wide = (reinterpret_cast<uintptr_t>(a.dk) & 31) == 0 && (reinterpret_cast<uintptr_t>(a.dv) & 31) == 0 &&
+               (packed || (a.dk_stride[0] % 16 == 0 && a.dv_stride[0] % 16 == 0)) && a.dk_stride[1] % 16 == 0 &&
+               a.dk_stride[2] % 16 == 0 && a.dv_stride[1] % 16 == 0 && a.dv_stride[2] % 16 == 0 && bp.head_dim % 16 == 0;
   p.work_list = nullptr;
   p.n_blocks = p.head_slots = p.section = 1;
   p.status = device_status_word();

@@ -30,6 +30,7 @@ struct BwdParams {
   float* pivot_sum;
   int* pivot_key;
   int head_dim;           // columns of the tensors (<= the compiled D; TMA zero-fills the columns in between)
+  int dkv_wide;           // 1: dK and dV rows may be written with 32-byte stores (alignment of bases and strides)
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;
   int64_t dk_batch_stride, dk_row_stride, dk_head_stride;

@@ -447,7 +447,16 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
             for (int i = 0; i < 32; ++i) acc[i] = 0;
           }
-          if (key_valid) {
+          if (key_valid && p.dkv_wide) {  // 32-byte stores: a lane writes whole sectors of its row
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              uint32_t w[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                w[j] = pack_bf16x2(__uint_as_float(acc[16 * i + 2 * j]) * mul, __uint_as_float(acc[16 * i + 2 * j + 1]) * mul);
+              if (dh * 128 + 32 * ch + 16 * i < p.head_dim) st_global_v8(dst + 4 * ch + 2 * i, w);
+            }
+          } else if (key_valid) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               uint4 v;
